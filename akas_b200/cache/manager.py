@@ -92,6 +92,7 @@ class _Group:
     page_size: int = 0
     max_blocks: int = 0  # columns of this group's block table: the pages a request of full context holds
     blocks: Dict[Hashable, List[int]] = field(default_factory=dict)  # request -> page per block, -1 once released
+    keep_first: int = 0  # tokens at a request's start that stay readable behind the window: their pages are kept
 
 
 @dataclass
@@ -149,7 +150,8 @@ class CacheManager:
                     gid = len(self.groups)
                     self._group_of[spec.paging()] = gid
                     self.groups.append(_Group(spec.window, PageAllocator(pool_tokens // size), page_size=size,
-                                              max_blocks=-(-context // size)))
+                                              max_blocks=-(-context // size),
+                                              keep_first=spec.keep_first if spec.window else 0))
                 pools = {name: None for name in spec.pools(size)}
                 if storage:
                     pages = self.groups[gid].allocator.num_pages
@@ -267,7 +269,8 @@ class CacheManager:
             # the next query sits at position `length` and sees keys >= length - window + 1
             first_needed = req.length - group.window + 1
             blocks = group.blocks[request]
-            for b in range(min(len(blocks), max(0, first_needed) // group.page_size)):
+            kept = -(-group.keep_first // group.page_size)  # blocks that hold tokens every later query still sees
+            for b in range(kept, min(len(blocks), max(0, first_needed) // group.page_size)):
                 if blocks[b] >= 0:
                     group.allocator.give(blocks[b])
                     blocks[b] = -1

@@ -1,6 +1,8 @@
 """Typed configurations and the architecture registry."""
 
 from .engine import EngineConfig
+from .gigusun import ARCHITECTURE as GIGUSUN_ARCHITECTURE
+from .gigusun import GigusunConfig
 from .lfm2 import ARCHITECTURE as LFM2_ARCHITECTURE
 from .lfm2 import ConfigError, Lfm2Config
 from .registry import (
@@ -12,9 +14,12 @@ from .registry import (
 )
 from .specs import (
     AttentionSpec,
+    GatedDeltaSpec,
+    GatedLinearAttentionSpec,
     LayerSpec,
     ModelSpec,
     PartSpec,
+    PolyNormMLPSpec,
     RMSNormSpec,
     RopeSpec,
     ScheduleEntry,
@@ -23,9 +28,11 @@ from .specs import (
 )
 
 register_architecture(LFM2_ARCHITECTURE, Lfm2Config, model_type="lfm2")
+register_architecture(GIGUSUN_ARCHITECTURE, GigusunConfig)
 
 __all__ = [
-    "AttentionSpec", "ConfigError", "EngineConfig", "LayerSpec", "Lfm2Config", "ModelSpec", "PartSpec",
+    "AttentionSpec", "ConfigError", "EngineConfig", "GatedDeltaSpec", "GatedLinearAttentionSpec", "GigusunConfig", "LayerSpec",
+    "Lfm2Config", "ModelSpec", "PartSpec", "PolyNormMLPSpec",
     "RMSNormSpec", "RopeSpec", "ScheduleEntry", "ShortConvSpec", "SwiGLUSpec", "architecture_of",
     "architectures", "config_from_dict", "load_config", "register_architecture",
 ]

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its typed configuration.
 
-``config.json["architectures"][0]`` (or, failing that, ``model_type``) picks the
-entry. The configuration class must offer ``from_dict(mapping)``, ``to_dict()``
+``config.json["architectures"][0]`` (or ``"architecture"``, or, failing that,
+``model_type``) picks the entry. The configuration class must offer ``from_dict(mapping)``, ``to_dict()``
 and ``model_spec() -> ModelSpec``; the engine builds every architecture from its
 ``ModelSpec`` with the same generic decoder, so registering a configuration class
 is all that a new architecture made of existing parts needs.
@@ -35,7 +35,9 @@ def architectures() -> tuple[str, ...]:
 
 
 def architecture_of(data: Mapping[str, Any]) -> str:
-    names = data.get("architectures") or []
+    names = list(data.get("architectures") or [])
+    if isinstance(data.get("architecture"), str):  # some model folders name their one architecture under this key
+        names.append(data["architecture"])
     for name in names:
         if name in _ARCHITECTURES:
             return name

@@ -64,6 +64,23 @@ class AttentionSpec:
     scale: Optional[float] = None  # None: head_dim ** -0.5
     kind: str = "attention"
     names: Mapping[str, str] = field(default_factory=dict)  # local parameter name -> name in the checkpoint
+    # Options that LFM2 leaves at their defaults. Any of them sends the layer to the general attention kernels.
+    v_head_dim: Optional[int] = None  # size of a value head; None: head_dim
+    softcap: Optional[float] = None  # score <- cap * tanh(score / cap), after the scale
+    distance_bias: bool = False  # score <- score - r1_h * ln(1 + r2_h * (i - j)); r1, r2 are two tensors [heads]
+    keep_first: int = 0  # with a window: the first keep_first positions of a request stay visible behind it
+    sink: bool = False  # one more term exp(0) in the softmax's denominator; it has no value
+    gate: Optional[str] = None  # "head": head h's output times sigmoid(W_g x)_h, W_g [heads, hidden], x the mixer's input
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+    @property
+    def general(self) -> bool:
+        """Whether the layer needs what only the general attention kernels compute."""
+        return bool(self.v_head_dim not in (None, self.head_dim) or self.softcap or self.distance_bias or self.keep_first
+                    or self.sink or self.gate)
 
 
 @dataclass(frozen=True)
@@ -88,6 +105,59 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class GatedLinearAttentionSpec:
+    """Linear attention with a decay per key channel: S <- diag(alpha) S + k v^T, o = S^T q, per head.
+
+    alpha = sigmoid(W_a2 (W_a1 x) + b)^(1 / tau) through a low-rank pair of matrices; q is scaled by
+    ``key_dim ** -0.5``; each head's o is RMS-normed over ``value_dim`` (plain weight shared by the heads) and the
+    concatenated heads are multiplied by silu(W_g x) before the output product."""
+
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay_rank: int
+    tau: float
+    norm_eps: float
+    kind: str = "gated_linear_attention"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, per head.
+
+    q and k (``num_kv_heads`` heads of ``key_dim``, shared by groups of value heads) and v pass a causal depthwise
+    convolution of ``conv_kernel`` taps and silu; q and k are then made unit vectors (``unit_eps`` under the root), q
+    times ``key_dim ** -0.5``. beta = sigmoid(W_b x); g = exp(-exp(A_log) * softplus(W_a x + dt_bias)), one per head.
+    Each head's o is divided by its root mean square over ``value_dim``, times a weight shared by the heads, times
+    silu(W_g x)."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_kernel: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    kind: str = "gated_delta"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class PolyNormMLPSpec:
+    """W_down act(W_up x), act(z) = a N(z) + b N(z^2) + c N(z^3) + e with N the division of a token's row by its
+    root mean square (``eps`` under the root) and a, b, c, e four learned numbers."""
+
+    hidden_size: int
+    intermediate_size: int
+    eps: float
+    kind: str = "polynorm_mlp"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which parts it holds, how they are arranged, and where its weights are.
 
@@ -96,13 +166,13 @@ class LayerSpec:
     """
 
     mixer: Any
-    ffn: Any
+    ffn: Any  # None: the layer has no feed-forward (and no norm for it)
     mixer_norm: Any
     ffn_norm: Any
     mixer_prefix: str
     ffn_prefix: str
     mixer_norm_name: str
-    ffn_norm_name: str
+    ffn_norm_name: Optional[str]
     arrangement: str = "pre_norm"
 
 
@@ -139,6 +209,11 @@ class ModelSpec:
     embedding_multiplier: Optional[float] = None
     logit_scale: Optional[float] = None
     logit_softcap: Optional[float] = None
+    # Learned absolute positions: row p of this tensor [max_context, hidden] is added to the embedding of the token at
+    # position p (after the multiplier). And a norm of the sum before the first block.
+    position_table_name: Optional[str] = None
+    embedding_norm: Any = None
+    embedding_norm_name: Optional[str] = None
 
     def run_order(self) -> Tuple[ScheduleEntry, ...]:
         if self.schedule:

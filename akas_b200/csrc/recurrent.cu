@@ -1,0 +1,387 @@
+// Mixers with a matrix state per head: gated linear attention and the gated delta rule, and what stands around
+// their recurrences (low-rank decay gates, a causal depthwise convolution with silu, unit-length q and k, the
+// step sizes and decays of the delta rule, the gated RMS norm of the read-out).
+//
+// Everything here is float32 arithmetic whatever the compute dtype; inputs that a matrix product wrote may be
+// bfloat16 and are widened on load. The recurrences run token by token in one fixed order per (request, head,
+// value channel), so a request's results do not depend on how its tokens were cut into steps or on what else
+// is in the batch.
+//
+// State layouts (one row per request slot; only the slot stride is free, so a state may be part of a wider
+// row): a matrix state is S^T, [heads, value_dim, key_dim] float32, so that the key channels a thread owns are
+// contiguous; a convolution's state is its last taps - 1 inputs, [taps - 1, channels] float32, oldest first.
+#include "common.cuh"
+
+using namespace akas;
+
+namespace {
+
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+// ------------------------------------------------------------------------------------------------ decay gates
+//
+// out[n, o] = sigmoid(z)^(1 / tau), z = sum_r low[n, r] * w[o, r] + bias[o]: the up projection of a low-rank pair in
+// float32 (one ascending chain of fused multiply-adds per output), then exp(log sigmoid(z) / tau).
+constexpr int kGateTokens = 8;
+
+template <typename T>
+__global__ void decay_gates_kernel(const T* __restrict__ low, long long ld, const float* __restrict__ w,
+                                   const float* __restrict__ bias, float* __restrict__ out, int N, int O, int R,
+                                   float inv_tau) {
+  extern __shared__ float rows[];  // [kGateTokens][R]
+  const int n0 = blockIdx.x * kGateTokens;
+  for (int i = threadIdx.x; i < kGateTokens * R; i += blockDim.x) {
+    const int t = i / R, r = i % R;
+    rows[i] = n0 + t < N ? to_f32(low[(size_t)(n0 + t) * ld + r]) : 0.f;
+  }
+  __syncthreads();
+  for (int o = blockIdx.y * blockDim.x + threadIdx.x; o < O; o += gridDim.y * blockDim.x) {
+    float acc[kGateTokens];
+#pragma unroll
+    for (int t = 0; t < kGateTokens; ++t) acc[t] = 0.f;
+    const float* wr = w + (size_t)o * R;
+    for (int r = 0; r < R; ++r) {
+      const float wv = wr[r];
+#pragma unroll
+      for (int t = 0; t < kGateTokens; ++t) acc[t] = fmaf(rows[t * R + r], wv, acc[t]);
+    }
+    const float b = bias[o];
+#pragma unroll
+    for (int t = 0; t < kGateTokens; ++t)
+      if (n0 + t < N) out[(size_t)(n0 + t) * O + o] = expf(-softplus_f(-(acc[t] + b)) * inv_tau);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ the recurrences
+//
+// One block per (head, request, tile of value channels). A thread owns R consecutive key channels of one value
+// channel j: s[r] = S[ks * R + r][j]; the KS threads of a value channel are neighbouring lanes of a warp and add
+// their partial sums by shuffles. The step's tokens come through shared memory in chunks of CH (fewer where rows are long).
+//
+//   GLA:    s <- alpha_t[kk] s + k_t[kk] v_t[j];                                  o_t[j] = sum_kk s q_t[kk]
+//   DELTA:  s <- g_t s; u = beta_t (v_t[j] - sum_kk s k_t[kk]); s <- s + k_t[kk] u; o_t[j] = sum_kk s q_t[kk]
+constexpr int kPad = 4;  // floats between the R-blocks of a shared row: neighbouring lanes' 16-byte reads miss each other's banks
+
+template <int KS> __device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = KS / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <typename T, int R, int KS, int CH, bool DELTA>
+__global__ void __launch_bounds__(256)
+scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk, const T* __restrict__ v,
+            long long ldv, const float* __restrict__ decay /* GLA: alpha [N, H * D]; DELTA: g [N, H] */,
+            const float* __restrict__ beta /* DELTA: [N, H] */, float* __restrict__ state, long long slot_stride,
+            const int* __restrict__ cu_seqlens, const int* __restrict__ slots, float* __restrict__ out, int H, int rep,
+            int D, int V, float q_scale, int write) {
+  constexpr int VT = 256 / KS;          // value channels of a block
+  constexpr int ROW = KS * (R + kPad);  // floats of a padded shared row of key channels
+  __shared__ __align__(16) float sq[CH][ROW];
+  __shared__ __align__(16) float sk[CH][ROW];
+  __shared__ __align__(16) float sa[DELTA ? 1 : CH][DELTA ? 4 : ROW];
+  __shared__ float sv[CH][VT];
+  __shared__ float sg[CH], sb[CH];
+
+  const int h = blockIdx.x, req = blockIdx.y;
+  const int slot = slots[req];
+  const int t_begin = cu_seqlens[req], t_end = cu_seqlens[req + 1];
+  if (slot < 0 || t_end <= t_begin) return;
+  const int ks = threadIdx.x % KS, jl = threadIdx.x / KS;
+  const int j = blockIdx.z * VT + jl;
+  const bool live = j < V;
+  const int hk = h / rep;  // the q/k head that this head reads
+  const int kk0 = ks * R;
+
+  float s[R];
+  float* srow = state + (size_t)slot * slot_stride + ((size_t)h * V + (live ? j : 0)) * D;
+  const bool vec = D % 4 == 0 && slot_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(state) & 15) == 0;
+#pragma unroll
+  for (int r = 0; r < R; r += 4) {
+    if (live && vec && kk0 + r + 3 < D) {
+      const float4 x = *reinterpret_cast<const float4*>(srow + kk0 + r);
+      s[r] = x.x; s[r + 1] = x.y; s[r + 2] = x.z; s[r + 3] = x.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[r + e] = live && kk0 + r + e < D ? srow[kk0 + r + e] : 0.f;
+    }
+  }
+
+  for (int c0 = t_begin; c0 < t_end; c0 += CH) {
+    const int count = min(CH, t_end - c0);
+    __syncthreads();  // the chunk before has been read
+    for (int i = threadIdx.x; i < count * KS * R; i += 256) {
+      const int t = i / (KS * R), kk = i % (KS * R);
+      const int at = kk + (kk / R) * kPad;
+      const bool in = kk < D;
+      const size_t n = (size_t)(c0 + t);
+      sq[t][at] = in ? to_f32(q[n * ldq + (size_t)hk * D + kk]) * q_scale : 0.f;
+      sk[t][at] = in ? to_f32(k[n * ldk + (size_t)hk * D + kk]) : 0.f;
+      if (!DELTA) sa[t][at] = in ? decay[n * ((size_t)H * D) + (size_t)h * D + kk] : 0.f;
+    }
+    for (int i = threadIdx.x; i < count * VT; i += 256) {
+      const int t = i / VT, jj = i % VT;
+      const int col = blockIdx.z * VT + jj;
+      sv[t][jj] = col < V ? to_f32(v[(size_t)(c0 + t) * ldv + (size_t)h * V + col]) : 0.f;
+    }
+    if (DELTA && threadIdx.x < count) {
+      sg[threadIdx.x] = decay[(size_t)(c0 + threadIdx.x) * H + h];
+      sb[threadIdx.x] = beta[(size_t)(c0 + threadIdx.x) * H + h];
+    }
+    __syncthreads();
+    for (int t = 0; t < count; ++t) {
+      const float* qr = &sq[t][ks * (R + kPad)];
+      const float* kr = &sk[t][ks * (R + kPad)];
+      const float vj = sv[t][jl];
+      float acc = 0.f;
+      if (DELTA) {
+        const float g = sg[t];
+        float pk = 0.f;
+#pragma unroll
+        for (int r = 0; r < R; r += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+          s[r] *= g; s[r + 1] *= g; s[r + 2] *= g; s[r + 3] *= g;
+          pk = fmaf(s[r], kv.x, pk); pk = fmaf(s[r + 1], kv.y, pk); pk = fmaf(s[r + 2], kv.z, pk); pk = fmaf(s[r + 3], kv.w, pk);
+        }
+        pk = group_sum<KS>(pk);
+        const float u = sb[t] * (vj - pk);
+#pragma unroll
+        for (int r = 0; r < R; r += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+          const float4 qv = *reinterpret_cast<const float4*>(qr + r);
+          s[r] = fmaf(kv.x, u, s[r]); s[r + 1] = fmaf(kv.y, u, s[r + 1]);
+          s[r + 2] = fmaf(kv.z, u, s[r + 2]); s[r + 3] = fmaf(kv.w, u, s[r + 3]);
+          acc = fmaf(s[r], qv.x, acc); acc = fmaf(s[r + 1], qv.y, acc); acc = fmaf(s[r + 2], qv.z, acc); acc = fmaf(s[r + 3], qv.w, acc);
+        }
+      } else {
+        const float* ar = &sa[t][ks * (R + kPad)];
+#pragma unroll
+        for (int r = 0; r < R; r += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+          const float4 qv = *reinterpret_cast<const float4*>(qr + r);
+          const float4 av = *reinterpret_cast<const float4*>(ar + r);
+          s[r] = fmaf(av.x, s[r], kv.x * vj); s[r + 1] = fmaf(av.y, s[r + 1], kv.y * vj);
+          s[r + 2] = fmaf(av.z, s[r + 2], kv.z * vj); s[r + 3] = fmaf(av.w, s[r + 3], kv.w * vj);
+          acc = fmaf(s[r], qv.x, acc); acc = fmaf(s[r + 1], qv.y, acc); acc = fmaf(s[r + 2], qv.z, acc); acc = fmaf(s[r + 3], qv.w, acc);
+        }
+      }
+      acc = group_sum<KS>(acc);
+      if (ks == 0 && live) out[(size_t)(c0 + t) * ((size_t)H * V) + (size_t)h * V + j] = acc;
+    }
+  }
+  if (write && live) {
+#pragma unroll
+    for (int r = 0; r < R; r += 4) {
+      if (vec && kk0 + r + 3 < D) {
+        *reinterpret_cast<float4*>(srow + kk0 + r) = make_float4(s[r], s[r + 1], s[r + 2], s[r + 3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (kk0 + r + e < D) srow[kk0 + r + e] = s[r + e];
+      }
+    }
+  }
+}
+
+template <typename T, bool DELTA>
+int launch_scan(const T* q, long long ldq, const T* k, long long ldk, const T* v, long long ldv, const float* decay,
+                const float* beta, float* state, long long slot_stride, const int* cu_seqlens, const int* slots, float* out,
+                int requests, int H, int rep, int D, int V, float q_scale, int write, cudaStream_t stream) {
+  if (requests <= 0 || H <= 0) return 0;
+  if (D > 1024) return (int)cudaErrorInvalidValue;
+#define AKAS_SCAN(R, KS, CH)                                                                                              \
+  {                                                                                                                       \
+    const dim3 grid(H, requests, (V + 256 / KS - 1) / (256 / KS));                                                        \
+    scan_kernel<T, R, KS, CH, DELTA><<<grid, 256, 0, stream>>>(q, ldq, k, ldk, v, ldv, decay, beta, state, slot_stride,   \
+                                                           cu_seqlens, slots, out, H, rep, D, V, q_scale, write);         \
+    return launch_status();                                                                                               \
+  }
+  if (D <= 8) AKAS_SCAN(8, 1, 16)
+  if (D <= 16) AKAS_SCAN(8, 2, 16)
+  if (D <= 32) AKAS_SCAN(8, 4, 16)
+  if (D <= 64) AKAS_SCAN(16, 4, 16)
+  if (D <= 128) AKAS_SCAN(16, 8, 16)
+  if (D <= 256) AKAS_SCAN(16, 16, 8)
+  if (D <= 512) AKAS_SCAN(16, 32, 4)
+  AKAS_SCAN(32, 32, 2)
+#undef AKAS_SCAN
+}
+
+// ------------------------------------------------------------------------------------------------ causal convolution
+//
+// y[n, c] = silu(sum_j taps[c, j] * x_(i - L + 1 + j)) for the i-th token of its request in this step; inputs before
+// the step's first token come from the request's state rows. One ascending chain of fused multiply-adds per output.
+template <typename T>
+__global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ taps,
+                                        const float* __restrict__ state, long long slot_stride,
+                                        const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token,
+                                        const int* __restrict__ slots, float* __restrict__ y, int C, int L) {
+  const int n = blockIdx.x;
+  const int req = seq_of_token[n];
+  if (req < 0) return;
+  const int slot = slots[req];
+  if (slot < 0) return;
+  const int first = cu_seqlens[req];
+  const int i = n - first;
+  const float* st = state + (size_t)slot * slot_stride;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < L; ++j) {
+      const int src = i - (L - 1) + j;
+      const float in = src >= 0 ? to_f32(x[(size_t)(first + src) * ldx + c]) : st[(size_t)(L - 1 + src) * C + c];
+      acc = fmaf(taps[(size_t)c * L + j], in, acc);
+    }
+    y[(size_t)n * C + c] = acc * sigmoid_f(acc);
+  }
+}
+
+// The state after the step: the last L - 1 inputs of each request, from the step's tokens and, where those are fewer,
+// from the rows the state held. Row i takes what is n_r rows further on, so ascending i never overwrites a row that
+// is still to be read.
+template <typename T>
+__global__ void causal_conv_state_kernel(const T* __restrict__ x, long long ldx, float* __restrict__ state,
+                                         long long slot_stride, const int* __restrict__ cu_seqlens,
+                                         const int* __restrict__ slots, int C, int L) {
+  const int req = blockIdx.x;
+  const int slot = slots[req];
+  const int first = cu_seqlens[req], count = cu_seqlens[req + 1] - first;
+  if (slot < 0 || count <= 0) return;
+  float* st = state + (size_t)slot * slot_stride;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+    for (int i = 0; i < L - 1; ++i) {
+      const int src = count - (L - 1) + i;  // index among the step's tokens
+      st[(size_t)i * C + c] = src >= 0 ? to_f32(x[(size_t)(first + src) * ldx + c]) : st[(size_t)(i + count) * C + c];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ delta rule inputs
+//
+// One block per token. Heads of q (the first G * D columns of y) and of k (the next G * D) become unit vectors,
+// x / sqrt(sum x^2 + unit_eps), q times q_scale too; beta = sigmoid(b); g = exp(-exp(A_log) * softplus(a + dt_bias)).
+template <typename T>
+__global__ void delta_prep_kernel(float* __restrict__ y, long long ldy, int G, int D, float q_scale, float unit_eps,
+                                  const T* __restrict__ b, long long ldb, const T* __restrict__ a, long long lda,
+                                  const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                  float* __restrict__ beta, float* __restrict__ g, int H) {
+  const int n = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int head = warp; head < 2 * G; head += warps) {
+    float* row = y + (size_t)n * ldy + (size_t)head * D;
+    float ss = 0.f;
+    for (int d = lane; d < D; d += 32) ss = fmaf(row[d], row[d], ss);
+    ss = warp_sum(ss);
+    const float inv = (head < G ? q_scale : 1.f) / sqrtf(ss + unit_eps);
+    for (int d = lane; d < D; d += 32) row[d] *= inv;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    beta[(size_t)n * H + h] = sigmoid_f(to_f32(b[(size_t)n * ldb + h]));
+    g[(size_t)n * H + h] = expf(-expf(a_log[h]) * softplus_f(to_f32(a[(size_t)n * lda + h]) + dt_bias[h]));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ gated RMS norm
+//
+// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * silu(gate).
+template <typename TG, typename TO>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
+                                     const TG* __restrict__ gate, long long ldg, TO* __restrict__ out, int N, int H, int V) {
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)N * H) return;
+  const int n = (int)(item / H), h = (int)(item % H);
+  const float* row = o + (size_t)n * H * V + (size_t)h * V;
+  float ss = 0.f;
+  for (int j = lane; j < V; j += 32) ss = fmaf(row[j], row[j], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)V + eps);
+  for (int j = lane; j < V; j += 32) {
+    const float gv = to_f32(gate[(size_t)n * ldg + (size_t)h * V + j]);
+    out[(size_t)n * H * V + (size_t)h * V + j] = from_f32<TO>(row[j] * inv * w[j] * (gv * sigmoid_f(gv)));
+  }
+}
+
+}  // namespace
+
+AKAS_API int akas_decay_gates(const void* low, long long ld, const float* w, const float* bias, float* out, int N, int O,
+                              int R, float tau, int dtype, cudaStream_t stream) {
+  if (N <= 0 || O <= 0) return 0;
+  const dim3 grid((N + kGateTokens - 1) / kGateTokens, min((O + 127) / 128, 64));
+  const size_t smem = (size_t)kGateTokens * R * sizeof(float);
+  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+  if (dtype == AKAS_F32)
+    decay_gates_kernel<float><<<grid, 128, smem, stream>>>((const float*)low, ld, w, bias, out, N, O, R, 1.f / tau);
+  else
+    decay_gates_kernel<bf16><<<grid, 128, smem, stream>>>((const bf16*)low, ld, w, bias, out, N, O, R, 1.f / tau);
+  return launch_status();
+}
+
+AKAS_API int akas_gla_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
+                           const float* alpha, float* state, long long slot_stride, const int* cu_seqlens, const int* slots,
+                           float* out, int requests, int H, int D, int V, float q_scale, int write, int dtype,
+                           cudaStream_t stream) {
+  if (dtype == AKAS_F32)
+    return launch_scan<float, false>((const float*)q, ldq, (const float*)k, ldk, (const float*)v, ldv, alpha, nullptr, state,
+                                     slot_stride, cu_seqlens, slots, out, requests, H, 1, D, V, q_scale, write, stream);
+  return launch_scan<bf16, false>((const bf16*)q, ldq, (const bf16*)k, ldk, (const bf16*)v, ldv, alpha, nullptr, state,
+                                  slot_stride, cu_seqlens, slots, out, requests, H, 1, D, V, q_scale, write, stream);
+}
+
+AKAS_API int akas_delta_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                             const float* beta, const float* g, float* state, long long slot_stride, const int* cu_seqlens,
+                             const int* slots, float* out, int requests, int H, int G, int D, int V, int write,
+                             cudaStream_t stream) {
+  if (G <= 0 || H % G) return (int)cudaErrorInvalidValue;
+  return launch_scan<float, true>(q, ldq, k, ldk, v, ldv, g, beta, state, slot_stride, cu_seqlens, slots, out, requests, H,
+                                  H / G, D, V, 1.f, write, stream);
+}
+
+AKAS_API int akas_causal_conv_silu(const void* x, long long ldx, const float* taps, float* state, long long slot_stride,
+                                   const int* cu_seqlens, const int* seq_of_token, const int* slots, float* y, int N,
+                                   int requests, int C, int L, int write, int dtype, cudaStream_t stream) {
+  if (N <= 0 || C <= 0) return 0;
+  const dim3 grid(N, min((C + 255) / 256, 32));
+  if (dtype == AKAS_F32)
+    causal_conv_silu_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, ldx, taps, state, slot_stride, cu_seqlens,
+                                                            seq_of_token, slots, y, C, L);
+  else
+    causal_conv_silu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)x, ldx, taps, state, slot_stride, cu_seqlens,
+                                                           seq_of_token, slots, y, C, L);
+  int err = launch_status();
+  if (err || !write || requests <= 0) return err;
+  const dim3 sgrid(requests, min((C + 255) / 256, 32));
+  if (dtype == AKAS_F32)
+    causal_conv_state_kernel<float><<<sgrid, 256, 0, stream>>>((const float*)x, ldx, state, slot_stride, cu_seqlens, slots, C, L);
+  else
+    causal_conv_state_kernel<bf16><<<sgrid, 256, 0, stream>>>((const bf16*)x, ldx, state, slot_stride, cu_seqlens, slots, C, L);
+  return launch_status();
+}
+
+AKAS_API int akas_delta_prep(float* y, long long ldy, int G, int D, float q_scale, float unit_eps, const void* b,
+                             long long ldb, const void* a, long long lda, const float* a_log, const float* dt_bias,
+                             float* beta, float* g, int N, int H, int dtype, cudaStream_t stream) {
+  if (N <= 0) return 0;
+  if (dtype == AKAS_F32)
+    delta_prep_kernel<float><<<N, 128, 0, stream>>>(y, ldy, G, D, q_scale, unit_eps, (const float*)b, ldb, (const float*)a,
+                                                    lda, a_log, dt_bias, beta, g, H);
+  else
+    delta_prep_kernel<bf16><<<N, 128, 0, stream>>>(y, ldy, G, D, q_scale, unit_eps, (const bf16*)b, ldb, (const bf16*)a, lda,
+                                                   a_log, dt_bias, beta, g, H);
+  return launch_status();
+}
+
+AKAS_API int akas_gated_rmsnorm(const float* o, const float* w, float eps, const void* gate, long long ldg, void* out, int N,
+                                int H, int V, int gate_dtype, int out_dtype, cudaStream_t stream) {
+  if (N <= 0 || H <= 0) return 0;
+  const long long items = (long long)N * H;
+  const int blocks = (int)((items + 7) / 8);
+#define AKAS_GN(TG, TO) \
+  gated_rmsnorm_kernel<TG, TO><<<blocks, 256, 0, stream>>>(o, w, eps, (const TG*)gate, ldg, (TO*)out, N, H, V)
+  if (gate_dtype == AKAS_F32 && out_dtype == AKAS_F32) AKAS_GN(float, float);
+  else if (gate_dtype == AKAS_F32) AKAS_GN(float, bf16);
+  else if (out_dtype == AKAS_F32) AKAS_GN(bf16, float);
+  else AKAS_GN(bf16, bf16);
+#undef AKAS_GN
+  return launch_status();
+}

@@ -1,6 +1,7 @@
 """The generic decoder that every registered architecture is built as.
 
-Embedding (times ``ModelSpec.embedding_multiplier`` if the architecture has one), the blocks of
+Embedding (times ``ModelSpec.embedding_multiplier`` if the architecture has one, plus a learned position vector
+and through a norm if it has those), the blocks of
 ``ModelSpec.layers`` in the order of ``ModelSpec.schedule`` (a list that may name a layer twice or let an
 entry read another entry's cache), the final norm on the rows whose logits are wanted, the head, and the
 architecture's ``logit_scale`` and ``logit_softcap`` if it has them. The head is the checkpoint's
@@ -41,7 +42,9 @@ class Decoder:
                         raise ValueError(f"schedule entry {i} reads the cache of entry {entry.cache}, but the mixer of layer "
                                          f"{which} ({type(mixer).__name__}) keeps a summary of the past that has moved on "
                                          "when a reader runs: give the entry a cache of its own")
+        self.embedding_norm = build_part("norm", spec.embedding_norm, runtime)
         self.embedding = None
+        self.positions = None  # learned absolute positions [max_context, hidden], where the architecture has them
         self.head = None
 
     # ------------------------------------------------------------------ weights
@@ -53,6 +56,11 @@ class Decoder:
         out[s.final_norm_name] = norm_param
         if s.head_name is not None:
             out[s.head_name] = Param((s.vocab_size, s.hidden_size), optional=s.head_optional)
+        if s.position_table_name is not None:
+            out[s.position_table_name] = Param((s.max_context, s.hidden_size))
+        if self.embedding_norm is not None:
+            (norm_param,) = self.embedding_norm.params().values()
+            out[s.embedding_norm_name] = norm_param
         for block in self.blocks:
             out.update(block.params())
         return out
@@ -61,6 +69,10 @@ class Decoder:
         s = self.spec
         self.embedding = get(s.embedding_name)
         self.final_norm.load(lambda _name: get(s.final_norm_name))
+        if s.position_table_name is not None:
+            self.positions = get(s.position_table_name)
+        if self.embedding_norm is not None:
+            self.embedding_norm.load(lambda _name: get(s.embedding_norm_name))
         self.head = get(s.head_name) if s.head_name is not None and has(s.head_name) else self.embedding
         for block in self.blocks:
             block.load(get)
@@ -89,6 +101,10 @@ class Decoder:
         h = ops.embedding(ctx.token_ids, self.embedding)
         if spec.embedding_multiplier is not None:
             h = ops.scale_cap(h, scale=spec.embedding_multiplier)
+        if self.positions is not None:
+            h = ops.add_rows(h, self.positions, ctx.positions)
+        if self.embedding_norm is not None:
+            h = self.embedding_norm.forward(h, out_dtype=torch.float32)  # the residual stream stays float32
         for i, entry in enumerate(self.schedule):
             owner = i if entry.cache is None else entry.cache
             block = self.blocks[entry.layer]

@@ -236,3 +236,190 @@ def take_tokens(token_ids, source, previous):
 
 def zero_rows(state, slot):
     state[:, slot].zero_()
+
+
+# --------------------------------------------------------------------------- learned positions, PolyNorm
+
+
+def add_rows(h, table, index):
+    """h[n] += table[index[n]] in place (h float32)."""
+    h += table[index.long()].to(torch.float32)
+    return h
+
+
+def polynorm(z, coeffs, eps, out_dtype):
+    """a N(z) + b N(z^2) + c N(z^3) + e per row, N(x) = x / sqrt(mean(x^2) + eps); coeffs = (a, b, c, e), float32."""
+    zf = z.to(torch.float64)
+    c = coeffs.to(torch.float64)
+
+    def unit(x):
+        return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
+
+    return (c[0] * unit(zf) + c[1] * unit(zf * zf) + c[2] * unit(zf ** 3) + c[3]).to(out_dtype)
+
+
+# --------------------------------------------------------------------------- recurrent mixers
+#
+# State layouts. A request's state row lives at ``state[slot]``; ``slots[r]`` is the slot of the step's request r
+# (-1: padding, touch nothing) and ``cu_seqlens`` gives the extent of its tokens. A matrix state is
+# ``[slots, heads, key_dim, value_dim]`` float32; a convolution's state ``[slots, taps - 1, channels]`` float32, oldest
+# row first. Both may be views into a wider row per slot (only the slot stride is free).
+
+
+def decay_gates(low, w_up, bias, tau):
+    """sigmoid(low . w_up^T + bias)^(1 / tau) in float32: [N, O] for low [N, R] (any float dtype), w_up [O, R]."""
+    z = low.to(torch.float64) @ w_up.to(torch.float64).T + bias.to(torch.float64)
+    return torch.exp(torch.nn.functional.logsigmoid(z) / tau).to(torch.float32)
+
+
+def _requests(cu_seqlens, slots):
+    cu = cu_seqlens.tolist()
+    for r, slot in enumerate(slots.tolist()):
+        if slot >= 0 and cu[r + 1] > cu[r]:
+            yield slot, cu[r], cu[r + 1]
+
+
+def gla_scan(q, k, v, alpha, state, cu_seqlens, slots, heads, dim, vdim, q_scale, write=True):
+    """Per request and head, token by token: S <- diag(alpha_t) S + k_t v_t^T; o_t = S^T (q_scale q_t).
+    q, k, alpha [N, heads * dim], v [N, heads * vdim] -> o float32 [N, heads * vdim]."""
+    n = q.shape[0]
+    o = torch.zeros((n, heads, vdim), dtype=torch.float32, device=q.device)
+    qf = q.to(torch.float64).reshape(n, heads, dim) * q_scale
+    kf = k.to(torch.float64).reshape(n, heads, dim)
+    vf = v.to(torch.float64).reshape(n, heads, vdim)
+    af = alpha.to(torch.float64).reshape(n, heads, dim)
+    for slot, a, b in _requests(cu_seqlens, slots):
+        s = state[slot].to(torch.float64)
+        for t in range(a, b):
+            s = af[t][:, :, None] * s + kf[t][:, :, None] * vf[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", s, qf[t]).to(torch.float32)
+        if write:
+            state[slot] = s.to(torch.float32)
+    return o.reshape(n, heads * vdim)
+
+
+def causal_conv_silu(x, taps, state, cu_seqlens, seq_of_token, slots, write=True):
+    """silu of a causal depthwise convolution over each request's tokens: y_t = silu(sum_j taps[:, j] x_(t - L + 1 + j)),
+    inputs before the step's first token from ``state`` (zero at a request's start). x [N, C] -> float32 [N, C]."""
+    n, c = x.shape
+    l = taps.shape[1]
+    xf = x.to(torch.float32)
+    out = torch.zeros((n, c), dtype=torch.float32, device=x.device)
+    for slot, a, b in _requests(cu_seqlens, slots):
+        hist = torch.cat((state[slot], xf[a:b]), dim=0)
+        acc = torch.zeros((b - a, c), dtype=torch.float32, device=x.device)
+        for j in range(l):
+            acc = acc + hist[j : j + b - a] * taps[:, j]
+        out[a:b] = acc * torch.sigmoid(acc)
+        if write:
+            state[slot] = hist[-(l - 1):]
+    return out
+
+
+def delta_prep(y, kv_heads, dim, q_scale, unit_eps, b, a, a_log, dt_bias):
+    """What the delta rule needs besides its convolved inputs. In place on float32 y [N, >= 2 kv_heads dim]: each
+    head of q (the first kv_heads * dim columns) and of k (the next) becomes x / sqrt(sum x^2 + unit_eps), q times
+    q_scale too. Returns (beta, g), float32 [N, H]: beta = sigmoid(b), g = exp(-exp(a_log) * softplus(a + dt_bias))."""
+    n = y.shape[0]
+    qk = y[:, : 2 * kv_heads * dim].reshape(n, 2 * kv_heads, dim).to(torch.float64)
+    qk = qk / torch.sqrt((qk * qk).sum(dim=-1, keepdim=True) + unit_eps)
+    qk[:, :kv_heads] *= q_scale
+    y[:, : 2 * kv_heads * dim] = qk.reshape(n, -1).to(torch.float32)
+    beta = torch.sigmoid(b.to(torch.float64)).to(torch.float32)
+    g = torch.exp(-torch.exp(a_log.to(torch.float64)) * torch.nn.functional.softplus(a.to(torch.float64) + dt_bias.to(torch.float64)))
+    return beta, g.to(torch.float32)
+
+
+def delta_scan(q, k, v, beta, g, state, cu_seqlens, slots, heads, kv_heads, dim, vdim, write=True):
+    """Per request and head, token by token: S <- g_t S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t.
+    q, k [N, kv_heads * dim] (head h reads q/k head h // (heads / kv_heads)), v [N, heads * vdim] -> o float32."""
+    n = q.shape[0]
+    rep = heads // kv_heads
+    o = torch.zeros((n, heads, vdim), dtype=torch.float32, device=q.device)
+    qf = q.to(torch.float64).reshape(n, kv_heads, dim).repeat_interleave(rep, dim=1)
+    kf = k.to(torch.float64).reshape(n, kv_heads, dim).repeat_interleave(rep, dim=1)
+    vf = v.to(torch.float64).reshape(n, heads, vdim)
+    bf, gf = beta.to(torch.float64), g.to(torch.float64)
+    for slot, a, b in _requests(cu_seqlens, slots):
+        s = state[slot].to(torch.float64)
+        for t in range(a, b):
+            s = gf[t][:, None, None] * s
+            u = bf[t][:, None] * (vf[t] - torch.einsum("hdv,hd->hv", s, kf[t]))
+            s = s + kf[t][:, :, None] * u[:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", s, qf[t]).to(torch.float32)
+        if write:
+            state[slot] = s.to(torch.float32)
+    return o.reshape(n, heads * vdim)
+
+
+def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype):
+    """Each head of o [N, heads * vdim] over its root mean square (eps under the root), times weight [vdim], times
+    silu(gate) [N, heads * vdim]."""
+    n = o.shape[0]
+    of = o.to(torch.float64).reshape(n, heads, vdim)
+    of = of / torch.sqrt((of * of).mean(dim=-1, keepdim=True) + eps) * weight.to(torch.float64)
+    gf = gate.to(torch.float64)
+    return (of.reshape(n, heads * vdim) * gf * torch.sigmoid(gf)).to(out_dtype)
+
+
+# --------------------------------------------------------------------------- general attention
+
+
+def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, k_pool, v_pool, block_table,
+                  seq_of_token, positions, page_size, write=True):
+    """Per-head RMSNorm (plain weight; None: no norm) of q [N, heads * dim] and k [N, kv_heads * dim]; the normed k
+    and v [N, kv_heads * vdim] go into the pages (k pages [.., kv_heads, page, dim], v pages [.., kv_heads, page,
+    vdim]); returns the normed q, contiguous, in the pools' dtype."""
+    n = q.shape[0]
+    qf = q.to(torch.float32).reshape(n, heads, dim)
+    kf = k.to(torch.float32).reshape(n, kv_heads, dim)
+    if q_weight is not None:
+        qf = rmsnorm(qf, q_weight, eps, False, torch.float32)
+        kf = rmsnorm(kf, k_weight, eps, False, torch.float32)
+    if write:
+        live, page, off = _page_addresses(block_table, seq_of_token, positions, page_size)
+        k_pool[page[live], :, off[live]] = kf[live].to(k_pool.dtype)
+        v_pool[page[live], :, off[live]] = v.reshape(n, kv_heads, vdim)[live].to(v_pool.dtype)
+    return qf.reshape(n, heads * dim).to(k_pool.dtype)
+
+
+def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
+                      r1, r2, sink, gate, page_size, ctx=None):
+    """Attention of every token over the keys of its request that it sees: j <= i and (no window, or i - j < window,
+    or j < keep_first). score = q . k * scale; with softcap, cap * tanh(score / cap); with r1 and r2 (float32
+    [heads]), minus r1_h * ln(1 + r2_h * (i - j)); softmax over the keys, with ``sink`` one more term exp(0) in the
+    denominator; the head's output times sigmoid(gate[n, h]) where ``gate`` [N, heads] is given.
+    q [N, heads * dim] -> [N, heads * vdim] in q's dtype."""
+    n = q.shape[0]
+    kh, d, vd = k_pool.shape[1], k_pool.shape[3], v_pool.shape[3]
+    heads = q.shape[1] // d
+    group = heads // kh
+    out = torch.zeros((n, heads, vd), dtype=torch.float64, device=q.device)
+    seqs, poss = seq_of_token.tolist(), positions.tolist()
+    for t in range(n):
+        r, p = seqs[t], poss[t]
+        if r < 0:
+            continue
+        idx = torch.arange(0, p + 1, device=q.device)
+        if window:
+            idx = idx[(p - idx < window) | (idx < keep_first)]
+        pages = block_table[r, idx // page_size].long()
+        offs = idx % page_size
+        keys = k_pool[pages, :, offs].to(torch.float64)  # [S, kh, d]
+        vals = v_pool[pages, :, offs].to(torch.float64)
+        qt = q[t].reshape(kh, group, d).to(torch.float64)
+        s = torch.einsum("kgd,skd->kgs", qt, keys) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        if r1 is not None:
+            dist = (p - idx).to(torch.float64)
+            s = s - r1.to(torch.float64).reshape(kh, group, 1) * torch.log1p(r2.to(torch.float64).reshape(kh, group, 1) * dist)
+        top = s.max(dim=-1, keepdim=True).values
+        if sink:
+            top = top.clamp(min=0.0)
+        e = torch.exp(s - top)
+        denom = e.sum(dim=-1, keepdim=True) + (torch.exp(-top) if sink else 0.0)
+        out[t] = torch.einsum("kgs,skd->kgd", e / denom, vals).reshape(heads, vd)
+    if gate is not None:
+        out = out * torch.sigmoid(gate.to(torch.float64))[:, :, None]
+    return out.reshape(n, heads * vd).to(q.dtype)

@@ -7,13 +7,19 @@ write of k and v into the pages at each token's absolute position (one kernel);
 attention of every query over the keys of its own request up to its own position,
 read from the pages, so a portion of a prompt attends to what earlier steps left
 and to itself; the output product, added to the residual.
+
+A layer whose spec asks for more than that (value heads of another size than the keys', a capped score, a
+logarithmic distance penalty, first tokens kept behind the window, a sink in the softmax's denominator, a gate
+per head on the output) runs the same steps on the general kernels: one product for q, k, v and the gate's
+logits, QK-norm and page write (``ops.qk_norm_store``), attention with the options as arguments
+(``ops.attention_general``), the output product.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .base import Mixer, PagedKVSpec, Param, build_part, project, register_mixer, renamed
+from .base import Mixer, PagedKVSpec, Param, build_part, project, register_mixer, renamed, stack_rows
 
 
 class Attention(Mixer):
@@ -26,26 +32,40 @@ class Attention(Mixer):
         s = spec
         if s.num_heads % s.num_kv_heads:
             raise ValueError(f"{s.num_heads} heads are not a multiple of {s.num_kv_heads} key/value heads")
-        if s.head_dim % 16 or s.head_dim > 256:
+        self.general = bool(getattr(s, "general", False))
+        if not self.general and (s.head_dim % 16 or s.head_dim > 256):
             raise ValueError(f"head_dim {s.head_dim} must be a multiple of 16, at most 256")
+        if self.general and s.position is not None:
+            raise ValueError("the general attention kernels take no position encoding of q and k")
+        if self.general and getattr(s, "gate", None) not in (None, "head"):
+            raise ValueError(f"unknown output gate {s.gate!r}; known: 'head'")
+        if self.general and s.keep_first and not s.window:
+            raise ValueError("keep_first needs a window")
         self.q_norm = build_part("norm", s.qk_norm, runtime)
         self.k_norm = build_part("norm", s.qk_norm, runtime)
         self.position = build_part("position", s.position, runtime)
         self.scale = s.scale if s.scale is not None else s.head_dim ** -0.5
         self.w_qkv = None
         self.w_out = None
+        self.r1 = self.r2 = None
 
     def _n(self, local):
         return renamed(self.spec, local)
 
     def params(self):
         s = self.spec
+        vd = s.value_dim if self.general else s.head_dim
         p = {
             self._n("q_proj.weight"): Param((s.num_heads * s.head_dim, s.hidden_size)),
             self._n("k_proj.weight"): Param((s.num_kv_heads * s.head_dim, s.hidden_size)),
-            self._n("v_proj.weight"): Param((s.num_kv_heads * s.head_dim, s.hidden_size)),
-            self._n("out_proj.weight"): Param((s.hidden_size, s.num_heads * s.head_dim)),
+            self._n("v_proj.weight"): Param((s.num_kv_heads * vd, s.hidden_size)),
+            self._n("out_proj.weight"): Param((s.hidden_size, s.num_heads * vd)),
         }
+        if self.general and s.gate == "head":
+            p[self._n("gate.weight")] = Param((s.num_heads, s.hidden_size))
+        if self.general and s.distance_bias:
+            p[self._n("r1")] = Param((s.num_heads,), role="vector")
+            p[self._n("r2")] = Param((s.num_heads,), role="vector", mean=0.5)
         if self.q_norm is not None:
             (norm_param,) = self.q_norm.params().values()
             p[self._n("q_norm.weight")] = norm_param
@@ -53,19 +73,54 @@ class Attention(Mixer):
         return p
 
     def load(self, get):
-        self.w_qkv = torch.cat(
-            [get(self._n("q_proj.weight")), get(self._n("k_proj.weight")), get(self._n("v_proj.weight"))], dim=0
-        ).contiguous()
+        if self.general:
+            parts = [get(self._n("q_proj.weight")), get(self._n("k_proj.weight")), get(self._n("v_proj.weight"))]
+            if self.spec.gate == "head":
+                parts.append(get(self._n("gate.weight")))
+            self.w_qkv = stack_rows(parts)
+            if self.spec.distance_bias:
+                self.r1, self.r2 = get(self._n("r1")), get(self._n("r2"))
+        else:
+            self.w_qkv = torch.cat(
+                [get(self._n("q_proj.weight")), get(self._n("k_proj.weight")), get(self._n("v_proj.weight"))], dim=0
+            ).contiguous()
         self.w_out = get(self._n("out_proj.weight"))
         if self.q_norm is not None:
             self.q_norm.weight = get(self._n("q_norm.weight"))
             self.k_norm.weight = get(self._n("k_norm.weight"))
 
     def cache(self):
-        return PagedKVSpec(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        s = self.spec
+        if self.general:
+            return PagedKVSpec(s.num_kv_heads, s.head_dim, s.window, keep_first=s.keep_first if s.window else 0,
+                               v_head_dim=s.value_dim)
+        return PagedKVSpec(s.num_kv_heads, s.head_dim, s.window)
+
+    def _forward_general(self, x, ctx, cache, residual, write):
+        s, ops = self.spec, self.rt.ops
+        proj = project(self.rt, x, self.w_qkv)
+        nq, nk, nv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.value_dim
+        q, k, v = proj[:, :nq], proj[:, nq : nq + nk], proj[:, nq + nk : nq + nk + nv]
+        gate = proj[:, nq + nk + nv : nq + nk + nv + s.num_heads] if s.gate == "head" else None
+        norm = self.q_norm.spec if self.q_norm is not None else None
+        if norm is not None and norm.zero_centered:
+            raise ValueError("the general attention kernels take a plain QK-norm weight")
+        table = ctx.block_table(cache.group)
+        qn = ops.qk_norm_store(
+            q, k, v, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
+            self.q_norm.weight if norm else None, self.k_norm.weight if norm else None, norm.eps if norm else 0.0,
+            cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, cache.page_size, write=write,
+        )
+        out = ops.attention_general(
+            qn, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, self.scale, s.window, s.keep_first,
+            s.softcap, self.r1, self.r2, s.sink, gate, cache.page_size, ctx,
+        )
+        return project(self.rt, out, self.w_out, residual=residual)
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):
         s, ops = self.spec, self.rt.ops
+        if self.general:
+            return self._forward_general(x, ctx, cache, residual, write)
         qkv = project(self.rt, x, self.w_qkv)
         fused = self.position is None or hasattr(self.position, "tables")
         cos = sin = None

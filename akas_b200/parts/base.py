@@ -39,13 +39,25 @@ class Param:
     convolution taps, biases) is held in float32; ``"table"`` is an integer table
     held in int32. ``optional`` tensors may be absent from the checkpoint. ``mean``
     is the mean that the random-weights mode draws the tensor around (1 for norm
-    weights).
+    weights). A size of -1 in ``shape`` is whatever the checkpoint has there (a size
+    that the configuration file does not give); ``default`` then names the size
+    that the random-weights mode uses.
     """
 
     shape: Tuple[int, ...]
     role: str = "matrix"
     optional: bool = False
     mean: float = 0.0
+    default: Tuple[int, ...] = ()
+
+    def fits(self, shape) -> bool:
+        return len(shape) == len(self.shape) and all(a in (-1, b) for a, b in zip(self.shape, shape))
+
+    def concrete(self) -> Tuple[int, ...]:
+        """The shape with every free size replaced by its default."""
+        if -1 in self.shape and len(self.default) != len(self.shape):
+            raise ValueError(f"a tensor of shape {self.shape} has a free size and no default for it")
+        return tuple(d if a == -1 else a for a, d in zip(self.shape, self.default or self.shape))
 
 
 class PagedSpec:
@@ -61,27 +73,31 @@ class PagedSpec:
     window: Optional[int] = None
     page_size: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    keep_first: int = 0  # with a window: the first keep_first tokens are read for ever, so their pages are never given back
 
     def pools(self, page_size: int) -> Dict[str, Tuple[int, ...]]:
         raise NotImplementedError
 
     def paging(self) -> tuple:
-        return (self.window, self.page_size)
+        return (self.window, self.page_size, self.keep_first if self.window else 0)
 
 
 @dataclass(frozen=True)
 class PagedKVSpec(PagedSpec):
-    """Keys and values of every position (or of the last ``window``), in pages ``[kv_heads, page, head_dim]``."""
+    """Keys and values of every position (or of the last ``window`` and the first ``keep_first``), in pages
+    ``[kv_heads, page, head_dim]`` (values: ``v_head_dim`` where that is given)."""
 
     num_kv_heads: int = 1
     head_dim: int = 16
     window: Optional[int] = None
     page_size: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    keep_first: int = 0
+    v_head_dim: Optional[int] = None
 
     def pools(self, page_size: int) -> Dict[str, Tuple[int, ...]]:
-        shape = (self.num_kv_heads, page_size, self.head_dim)
-        return {"k": shape, "v": shape}
+        return {"k": (self.num_kv_heads, page_size, self.head_dim),
+                "v": (self.num_kv_heads, page_size, self.v_head_dim or self.head_dim)}
 
 
 @dataclass(frozen=True)
@@ -211,6 +227,16 @@ def build_part(family: str, spec, runtime: Runtime):
     if kind not in table:
         raise KeyError(f"no {family} registered for kind {kind!r}; registered: {sorted(table)}")
     return table[kind](spec, runtime)
+
+
+def stack_rows(matrices, multiple: int = 16) -> torch.Tensor:
+    """Matrices [o_i, K] that multiply the same input, stacked into one [sum o_i rounded up to ``multiple``, K] (the
+    added rows are zero), so that one product feeds them all and its rows have a pitch that every product kernel writes."""
+    rows = sum(m.shape[0] for m in matrices)
+    pad = -rows % multiple
+    if pad:
+        matrices = list(matrices) + [torch.zeros((pad, matrices[0].shape[1]), dtype=matrices[0].dtype, device=matrices[0].device)]
+    return torch.cat(list(matrices), dim=0).contiguous()
 
 
 def renamed(spec, local: str) -> str:

@@ -33,7 +33,7 @@ def random_tensors(config, seed: int, std: float = 0.02, dtype: str = "bfloat16"
             continue
         if param.role == "table":
             raise ValueError(f"{name}: no rule for a random integer table")
-        value = torch.randn(param.shape, generator=gen, dtype=torch.float32) * std + param.mean
+        value = torch.randn(param.concrete(), generator=gen, dtype=torch.float32) * std + param.mean
         out[name] = value.to(store).contiguous()
     return out
 
