@@ -241,3 +241,57 @@ AKAS_API int akas_scale_cap(float* x, float scale, float cap, long long total, c
   scale_cap_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, scale, cap, (size_t)total);
   return launch_status();
 }
+
+// h[n, :] += float(table[index[n], :]) in place on float32 h: learned absolute positions on top of the embedding.
+template <typename T>
+__global__ void add_rows_kernel(float* __restrict__ h, const T* __restrict__ table, const int* __restrict__ index, int C) {
+  const int n = blockIdx.x;
+  const T* row = table + (size_t)index[n] * C;
+  float* dst = h + (size_t)n * C;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) dst[c] += to_f32(row[c]);
+}
+
+AKAS_API int akas_add_rows(float* h, const void* table, const int* index, int N, int C, int dtype, cudaStream_t stream) {
+  if (N <= 0) return 0;
+  const int threads = C >= 1024 ? 256 : 128;
+  if (dtype == AKAS_F32) add_rows_kernel<float><<<N, threads, 0, stream>>>(h, (const float*)table, index, C);
+  else add_rows_kernel<bf16><<<N, threads, 0, stream>>>(h, (const bf16*)table, index, C);
+  return launch_status();
+}
+
+// PolyNorm on float32 rows: out = a N(z) + b N(z^2) + c N(z^3) + e with N(x) = x / sqrt(mean(x^2) + eps) over the row
+// and the powers taken element by element; coeffs = (a, b, c, e). One block per row, float32 sums.
+template <typename TO>
+__global__ void polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coeffs, float eps,
+                                TO* __restrict__ out, int F) {
+  __shared__ float scratch[32];
+  const float* row = z + (size_t)blockIdx.x * F;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int c = threadIdx.x; c < F; c += blockDim.x) {
+    const float x = row[c], x2 = x * x, x3 = x2 * x;
+    s1 = fmaf(x, x, s1);
+    s2 = fmaf(x2, x2, s2);
+    s3 = fmaf(x3, x3, s3);
+  }
+  s1 = block_sum(s1, scratch);
+  s2 = block_sum(s2, scratch);
+  s3 = block_sum(s3, scratch);
+  const float i1 = coeffs[0] / sqrtf(s1 / (float)F + eps);
+  const float i2 = coeffs[1] / sqrtf(s2 / (float)F + eps);
+  const float i3 = coeffs[2] / sqrtf(s3 / (float)F + eps);
+  const float e = coeffs[3];
+  TO* dst = out + (size_t)blockIdx.x * F;
+  for (int c = threadIdx.x; c < F; c += blockDim.x) {
+    const float x = row[c], x2 = x * x;
+    dst[c] = from_f32<TO>(fmaf(x, i1, fmaf(x2, i2, fmaf(x2 * x, i3, e))));
+  }
+}
+
+AKAS_API int akas_polynorm(const float* z, const float* coeffs, float eps, void* out, int N, int F, int out_dtype,
+                           cudaStream_t stream) {
+  if (N <= 0) return 0;
+  const int threads = F >= 2048 ? 512 : 256;
+  if (out_dtype == AKAS_F32) polynorm_kernel<float><<<N, threads, 0, stream>>>(z, coeffs, eps, (float*)out, F);
+  else polynorm_kernel<bf16><<<N, threads, 0, stream>>>(z, coeffs, eps, (bf16*)out, F);
+  return launch_status();
+}

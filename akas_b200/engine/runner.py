@@ -34,8 +34,9 @@ _TOKEN_ROUNDING = 256
 _SHAPE_REPEATS, _SHAPE_GRAPHS = 3, 4  # a step shape is captured when it comes the third time; at most four are kept
 
 
-def default_ops(device: torch.device, dtype: torch.dtype):
-    """The compiled sm_100a kernels. There is no other product path: anything else fails here."""
+def default_ops(device: torch.device, dtype: torch.dtype, parts=()):
+    """The compiled sm_100a kernels, built for the kinds of parts the model holds. There is no other product path:
+    anything else fails here."""
     if device.type != "cuda":
         raise RuntimeError(
             f"akas_b200 runs on CUDA devices only (got {device}); pass ops=akas_b200.ops.reference "
@@ -43,8 +44,22 @@ def default_ops(device: torch.device, dtype: torch.dtype):
         )
     from ..ops import cuda as cuda_ops
 
-    cuda_ops.require(cuda_ops.libraries_for(dtype))
+    cuda_ops.require(cuda_ops.libraries_for(dtype, parts))
     return cuda_ops
+
+
+def kernel_kinds(spec) -> tuple:
+    """The kinds of kernels that the mixers of a model ask for (``Mixer.kernels``), each once, in layer order: what is
+    compiled before the first step, and no more."""
+    from ..parts.base import mixer_class
+
+    kinds = []
+    for layer in spec.layers:
+        kernels = getattr(mixer_class(layer.mixer), "kernels", None)  # (a mixer from outside may not say: it asks for none)
+        for kind in (kernels(layer.mixer) if kernels is not None else ()):
+            if kind not in kinds:
+                kinds.append(kind)
+    return tuple(kinds)
 
 
 class ModelRunner:
@@ -52,9 +67,9 @@ class ModelRunner:
         self.config = config or EngineConfig()
         self.device = torch.device(self.config.device)
         self.dtype = _DTYPES[self.config.dtype]
-        self.ops = ops if ops is not None else default_ops(self.device, self.dtype)
         self.model_config = model_config if model_config is not None else load_config(model_dir)
         spec = self.model_config.model_spec()
+        self.ops = ops if ops is not None else default_ops(self.device, self.dtype, kernel_kinds(spec))
         self.runtime = Runtime(self.dtype, self.device, self.ops)
         self.model = Decoder(spec, self.runtime)
         self.weight_bytes = load_weights(self.model, model_dir)

@@ -36,6 +36,29 @@ _SIGNATURES = {
         "akas_zero_row": [c_void_p, c_longlong, c_int, c_int, c_longlong, c_void_p],
         "akas_add_bias": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_scale_cap": [c_void_p, c_float, c_float, c_longlong, c_void_p],
+        "akas_add_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_polynorm": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+    },
+    "recurrent": {
+        "akas_decay_gates": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "akas_gla_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+        "akas_delta_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                            c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_causal_conv_silu": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_delta_prep": [c_void_p, c_longlong, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_void_p, c_longlong,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_gated_rmsnorm": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p],
+    },
+    "attention_general": {
+        "akas_qk_norm_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_void_p],
+        "akas_attention_general": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
+                                   c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_int, c_void_p],
     },
     "conv": {
         "akas_short_conv": [c_void_p] * 8 + [c_int] * 6 + [c_void_p],
@@ -138,14 +161,19 @@ _SIGNATURES = {
 _functions = {}
 
 
-def libraries_for(dtype: torch.dtype) -> list:
+def libraries_for(dtype: torch.dtype, parts: Iterable[str] = ("attention", "short_conv")) -> list:
     """The kernel files a model of this compute dtype needs under the switches as they stand: what a first call
-    compiles. A file that only a switch's other value needs (the library arm of the products, the tcgen05 decode
-    products, the decode chain) is built when that value is first used."""
-    names = ["elementwise", "conv", "rope", "attention", "sampling"]
+    compiles. ``parts``: the kinds of kernels its mixers asked for (``Part.kernels``); the default is LFM2's. A file
+    that only a switch's other value needs (the library arm of the products, the tcgen05 decode products, the decode
+    chain) is built when that value is first used."""
+    names = ["elementwise", "sampling"]
+    for kind in parts:
+        for name in _PART_FILES[kind](dtype):
+            if name not in names:
+                names.append(name)
     if dtype == torch.float32:
         return names + ["sgemm"]
-    names += ["gemm_tcgen05", "gemm_pair", "gemm_rows", "skinny_gemm", "attention_prefill", "attention_prefill_tc", "attention_decode"]
+    names += ["gemm_tcgen05", "gemm_pair", "gemm_rows", "skinny_gemm"]
     if products == "library":
         names.append("gemm_bf16")
     if decode_products == "stream":
@@ -153,6 +181,15 @@ def libraries_for(dtype: torch.dtype) -> list:
     if decode_chain == "1":
         names.append("decode_chain")
     return names
+
+
+_PART_FILES = {
+    "attention": lambda dtype: ["rope", "attention"] + (["attention_prefill", "attention_prefill_tc", "attention_decode"]
+                                                        if dtype == torch.bfloat16 else []),
+    "short_conv": lambda dtype: ["conv"],
+    "attention_general": lambda dtype: ["attention_general"],
+    "recurrent": lambda dtype: ["recurrent"],
+}
 
 
 def require(names: Optional[Iterable[str]] = None) -> None:
@@ -1043,6 +1080,171 @@ def paged_attention(q, k_pool, v_pool, block_table, seq_of_token, positions, sca
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
         _ptr(positions), _ptr(out), float(scale), win, page_size, n, heads, kh, d, _code(q), _stream()),
         "paged_attention")
+    return out
+
+
+# --------------------------------------------------------------------------- learned positions, PolyNorm
+
+
+@_flushes
+def add_rows(h, table, index):
+    """h[n] += table[index[n]] in place on float32 h [N, C]."""
+    n, c = h.shape
+    if h.dtype != torch.float32 or table.shape[1] != c:
+        raise ValueError("add_rows takes float32 h [N, C] and a table [rows, C]")
+    _check(_fn("elementwise", "akas_add_rows")(_ptr(_dense(h, "h")), _ptr(_dense(table, "table")), _ptr(index), n, c,
+                                              _code(table), _stream()), "add_rows")
+    return h
+
+
+@_flushes
+def polynorm(z, coeffs, eps, out_dtype):
+    """a N(z) + b N(z^2) + c N(z^3) + e per row of float32 z [N, F]; coeffs = (a, b, c, e) float32."""
+    n, f = z.shape
+    if z.dtype != torch.float32 or coeffs.dtype != torch.float32 or coeffs.numel() != 4:
+        raise ValueError("polynorm takes float32 z [N, F] and four float32 coefficients")
+    out = torch.empty((n, f), dtype=out_dtype, device=z.device)
+    _check(_fn("elementwise", "akas_polynorm")(_ptr(_dense(z, "z")), _ptr(coeffs), float(eps), _ptr(out), n, f,
+                                              _CODE[out_dtype], _stream()), "polynorm")
+    return out
+
+
+# --------------------------------------------------------------------------- mixers with a matrix state
+
+
+def _rows(t: torch.Tensor, what: str):
+    """(pointer, row pitch in elements) of a 2-D tensor whose rows are dense: a slice of columns of a product's result."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError(f"{what} must be two-dimensional with unit inner stride")
+    return t.data_ptr(), t.stride(0)
+
+
+def _slot_rows(state: torch.Tensor, what: str):
+    """(pointer, slot pitch in floats) of a float32 state [slots, ...] whose every slot is dense."""
+    if state.dtype != torch.float32 or not state[0].is_contiguous():
+        raise ValueError(f"{what} must be float32 with a dense row per slot")
+    return state.data_ptr(), state.stride(0)
+
+
+@_flushes
+def decay_gates(low, w_up, bias, tau):
+    """sigmoid(low . w_up^T + bias)^(1 / tau), float32 [N, O], for low [N, R] (a slice of a product's result) and
+    float32 w_up [O, R]."""
+    n, r = low.shape
+    o = w_up.shape[0]
+    if w_up.dtype != torch.float32 or bias.dtype != torch.float32 or w_up.shape[1] != r:
+        raise ValueError("decay_gates takes a float32 matrix [O, R] and bias [O]")
+    ptr, ld = _rows(low, "low")
+    out = torch.empty((n, o), dtype=torch.float32, device=low.device)
+    _check(_fn("recurrent", "akas_decay_gates")(ptr, ld, _ptr(_dense(w_up, "w_up")), _ptr(bias), _ptr(out), n, o, r, float(tau),
+                                               _code(low), _stream()), "decay_gates")
+    return out
+
+
+@_flushes
+def gla_scan(q, k, v, alpha, state, cu_seqlens, slots, heads, dim, vdim, q_scale, write=True):
+    n = q.shape[0]
+    if q.dtype != k.dtype or q.dtype != v.dtype or alpha.dtype != torch.float32 or not alpha.is_contiguous():
+        raise ValueError("gla_scan takes q, k, v of one dtype and a dense float32 alpha")
+    (qp, ldq), (kp, ldk), (vp, ldv) = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
+    sp, stride = _slot_rows(state, "state")
+    out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
+    _check(_fn("recurrent", "akas_gla_scan")(qp, ldq, kp, ldk, vp, ldv, _ptr(alpha), sp, stride, _ptr(cu_seqlens), _ptr(slots),
+                                            _ptr(out), slots.numel(), heads, dim, vdim, float(q_scale), int(bool(write)),
+                                            _code(q), _stream()), "gla_scan")
+    return out
+
+
+@_flushes
+def causal_conv_silu(x, taps, state, cu_seqlens, seq_of_token, slots, write=True):
+    n, c = x.shape
+    l = taps.shape[1]
+    if taps.dtype != torch.float32 or taps.shape[0] != c or not taps.is_contiguous():
+        raise ValueError("causal_conv_silu takes dense float32 taps [C, L]")
+    xp, ldx = _rows(x, "x")
+    sp, stride = _slot_rows(state, "state")
+    y = torch.empty((n, c), dtype=torch.float32, device=x.device)
+    _check(_fn("recurrent", "akas_causal_conv_silu")(xp, ldx, _ptr(taps), sp, stride, _ptr(cu_seqlens), _ptr(seq_of_token),
+                                                    _ptr(slots), _ptr(y), n, slots.numel(), c, l, int(bool(write)), _code(x),
+                                                    _stream()), "causal_conv_silu", kernels=2 if write else 1)
+    return y
+
+
+@_flushes
+def delta_prep(y, kv_heads, dim, q_scale, unit_eps, b, a, a_log, dt_bias):
+    n = y.shape[0]
+    h = b.shape[1]
+    if y.dtype != torch.float32 or b.dtype != a.dtype:
+        raise ValueError("delta_prep takes float32 y and b, a of one dtype")
+    yp, ldy = _rows(y, "y")
+    (bp, ldb), (ap, lda) = _rows(b, "b"), _rows(a, "a")
+    beta = torch.empty((n, h), dtype=torch.float32, device=y.device)
+    g = torch.empty_like(beta)
+    _check(_fn("recurrent", "akas_delta_prep")(yp, ldy, kv_heads, dim, float(q_scale), float(unit_eps), bp, ldb, ap, lda,
+                                              _ptr(a_log), _ptr(dt_bias), _ptr(beta), _ptr(g), n, h, _code(b), _stream()),
+           "delta_prep")
+    return beta, g
+
+
+@_flushes
+def delta_scan(q, k, v, beta, g, state, cu_seqlens, slots, heads, kv_heads, dim, vdim, write=True):
+    n = q.shape[0]
+    if any(t.dtype != torch.float32 for t in (q, k, v, beta, g)) or not beta.is_contiguous() or not g.is_contiguous():
+        raise ValueError("delta_scan takes float32 inputs")
+    (qp, ldq), (kp, ldk), (vp, ldv) = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
+    sp, stride = _slot_rows(state, "state")
+    out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
+    _check(_fn("recurrent", "akas_delta_scan")(qp, ldq, kp, ldk, vp, ldv, _ptr(beta), _ptr(g), sp, stride, _ptr(cu_seqlens),
+                                              _ptr(slots), _ptr(out), slots.numel(), heads, kv_heads, dim, vdim,
+                                              int(bool(write)), _stream()), "delta_scan")
+    return out
+
+
+@_flushes
+def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype):
+    n = o.shape[0]
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.shape[1] != heads * vdim:
+        raise ValueError("gated_rmsnorm takes dense float32 o [N, heads * vdim]")
+    gp, ldg = _rows(gate, "gate")
+    out = torch.empty((n, heads * vdim), dtype=out_dtype, device=o.device)
+    _check(_fn("recurrent", "akas_gated_rmsnorm")(_ptr(o), _ptr(weight), float(eps), gp, ldg, _ptr(out), n, heads, vdim,
+                                                 _code(gate), _CODE[out_dtype], _stream()), "gated_rmsnorm")
+    return out
+
+
+# --------------------------------------------------------------------------- general attention
+
+
+@_flushes
+def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, k_pool, v_pool, block_table,
+                  seq_of_token, positions, page_size, write=True):
+    n = q.shape[0]
+    if not (q.dtype == k.dtype == v.dtype == k_pool.dtype == v_pool.dtype):
+        raise TypeError("qk_norm_store: q, k, v and the pages must have one dtype")
+    (qp, ldq), (kp, ldk), (vp, ldv) = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
+    out = torch.empty((n, heads * dim), dtype=q.dtype, device=q.device)
+    _check(_fn("attention_general", "akas_qk_norm_store")(
+        qp, ldq, kp, ldk, vp, ldv, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(out), _ptr(k_pool), _ptr(v_pool),
+        _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions), page_size, n, heads, kv_heads, dim, vdim,
+        int(bool(write)), _code(q), _stream()), "qk_norm_store")
+    return out
+
+
+@_flushes
+def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
+                      r1, r2, sink, gate, page_size, ctx=None):
+    n = q.shape[0]
+    kh, d, vd = k_pool.shape[1], k_pool.shape[3], v_pool.shape[3]
+    heads = q.shape[1] // d
+    _dense(q, "q")
+    if q.dtype != k_pool.dtype or (gate is not None and gate.dtype != q.dtype):
+        raise TypeError("attention_general: q, the pages and the gate must have one dtype")
+    gp, ldg = _rows(gate, "gate") if gate is not None else (None, 0)
+    out = torch.empty((n, heads * vd), dtype=q.dtype, device=q.device)
+    _check(_fn("attention_general", "akas_attention_general")(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions),
+        _ptr(out), float(scale), int(window or 0), int(keep_first or 0), float(softcap or 0.0), _ptr(r1), _ptr(r2),
+        int(bool(sink)), gp, ldg, page_size, n, heads, kh, d, vd, _code(q), _stream()), "attention_general")
     return out
 
 

@@ -261,8 +261,9 @@ def polynorm(z, coeffs, eps, out_dtype):
 # --------------------------------------------------------------------------- recurrent mixers
 #
 # State layouts. A request's state row lives at ``state[slot]``; ``slots[r]`` is the slot of the step's request r
-# (-1: padding, touch nothing) and ``cu_seqlens`` gives the extent of its tokens. A matrix state is
-# ``[slots, heads, key_dim, value_dim]`` float32; a convolution's state ``[slots, taps - 1, channels]`` float32, oldest
+# (-1: padding, touch nothing) and ``cu_seqlens`` gives the extent of its tokens. A matrix state is a head's S
+# transposed, ``[slots, heads, value_dim, key_dim]`` float32 (the kernels' threads own runs of key channels); a
+# convolution's state ``[slots, taps - 1, channels]`` float32, oldest
 # row first. Both may be views into a wider row per slot (only the slot stride is free).
 
 
@@ -291,8 +292,8 @@ def gla_scan(q, k, v, alpha, state, cu_seqlens, slots, heads, dim, vdim, q_scale
     for slot, a, b in _requests(cu_seqlens, slots):
         s = state[slot].to(torch.float64)
         for t in range(a, b):
-            s = af[t][:, :, None] * s + kf[t][:, :, None] * vf[t][:, None, :]
-            o[t] = torch.einsum("hdv,hd->hv", s, qf[t]).to(torch.float32)
+            s = af[t][:, None, :] * s + vf[t][:, :, None] * kf[t][:, None, :]
+            o[t] = torch.einsum("hvd,hd->hv", s, qf[t]).to(torch.float32)
         if write:
             state[slot] = s.to(torch.float32)
     return o.reshape(n, heads * vdim)
@@ -344,9 +345,9 @@ def delta_scan(q, k, v, beta, g, state, cu_seqlens, slots, heads, kv_heads, dim,
         s = state[slot].to(torch.float64)
         for t in range(a, b):
             s = gf[t][:, None, None] * s
-            u = bf[t][:, None] * (vf[t] - torch.einsum("hdv,hd->hv", s, kf[t]))
-            s = s + kf[t][:, :, None] * u[:, None, :]
-            o[t] = torch.einsum("hdv,hd->hv", s, qf[t]).to(torch.float32)
+            u = bf[t][:, None] * (vf[t] - torch.einsum("hvd,hd->hv", s, kf[t]))
+            s = s + u[:, :, None] * kf[t][:, None, :]
+            o[t] = torch.einsum("hvd,hd->hv", s, qf[t]).to(torch.float32)
         if write:
             state[slot] = s.to(torch.float32)
     return o.reshape(n, heads * vdim)

@@ -27,6 +27,10 @@ class Attention(Mixer):
     chain_safe = True
     shares_cache = True
 
+    @classmethod
+    def kernels(cls, spec):
+        return ("attention_general",) if getattr(spec, "general", False) else ("attention",)
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         s = spec

@@ -183,6 +183,12 @@ class Mixer(Part):
     # past in a step of one token than in a step of many. The decoder refuses a run order that shares such a cache.
     shares_cache = False
 
+    @classmethod
+    def kernels(cls, spec) -> tuple:
+        """The kinds of compiled kernels a mixer of this spec launches (keys of ``ops.cuda._PART_FILES``), so that a
+        model's first call builds what it needs and nothing else. A mixer that names none uses the products only."""
+        return ()
+
     def cache(self):
         return None
 
@@ -216,6 +222,14 @@ def register_norm(kind: str, cls: type) -> None:
 
 def register_position(kind: str, cls: type) -> None:
     _register("position", kind, cls)
+
+
+def mixer_class(spec) -> type:
+    """The class registered for a mixer spec's kind."""
+    kind = getattr(spec, "kind", None)
+    if kind not in _REGISTRIES["mixer"]:
+        raise KeyError(f"no mixer registered for kind {kind!r}; registered: {sorted(_REGISTRIES['mixer'])}")
+    return _REGISTRIES["mixer"][kind]
 
 
 def build_part(family: str, spec, runtime: Runtime):

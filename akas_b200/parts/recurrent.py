@@ -25,6 +25,10 @@ class GatedLinearAttention(Mixer):
     takes_normed = True
     chain_safe = True
 
+    @classmethod
+    def kernels(cls, spec):
+        return ("recurrent",)
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.w_in = self.w_out = self.w_up = self.b_up = self.norm = None
@@ -62,7 +66,7 @@ class GatedLinearAttention(Mixer):
 
     def cache(self):
         s = self.spec
-        return StateSpec((s.num_heads, s.key_dim, s.value_dim), torch.float32)
+        return StateSpec((s.num_heads, s.value_dim, s.key_dim), torch.float32)  # S transposed, as the scan kernels keep it
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):
         s, ops = self.spec, self.rt.ops
@@ -81,6 +85,10 @@ class GatedLinearAttention(Mixer):
 class GatedDelta(Mixer):
     takes_normed = True
     chain_safe = True
+
+    @classmethod
+    def kernels(cls, spec):
+        return ("recurrent",)
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -122,17 +130,19 @@ class GatedDelta(Mixer):
         self.w_out = get(self._n("o"))
 
     def cache(self):
-        """One float32 row per slot: the convolution's last inputs [taps - 1, channels], then S [heads, key_dim, value_dim]."""
+        """One float32 row per slot: S transposed [heads, value_dim, key_dim], then the convolution's last inputs
+        [taps - 1, channels]; the row's length is rounded up to 4 floats so that every slot's S starts on 16 bytes."""
         s = self.spec
-        return StateSpec(((s.conv_kernel - 1) * self.channels + s.num_heads * s.key_dim * s.value_dim,), torch.float32)
+        words = s.num_heads * s.key_dim * s.value_dim + (s.conv_kernel - 1) * self.channels
+        return StateSpec((-(-words // 4) * 4,), torch.float32)
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):
         s, ops = self.spec, self.rt.ops
         gd, hv, h, ch = s.num_kv_heads * s.key_dim, s.num_heads * s.value_dim, s.num_heads, self.channels
         slots = cache.state.shape[0]
-        conv_words = (s.conv_kernel - 1) * ch
-        conv_state = cache.state[:, :conv_words].view(slots, s.conv_kernel - 1, ch)
-        matrix_state = cache.state[:, conv_words:].view(slots, h, s.key_dim, s.value_dim)
+        matrix_words = h * s.value_dim * s.key_dim
+        matrix_state = cache.state[:, :matrix_words].view(slots, h, s.value_dim, s.key_dim)
+        conv_state = cache.state[:, matrix_words : matrix_words + (s.conv_kernel - 1) * ch].view(slots, s.conv_kernel - 1, ch)
         proj = project(self.rt, x, self.w_in)
         y = ops.causal_conv_silu(proj[:, :ch], self.taps, conv_state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots, write=write)
         beta, g = ops.delta_prep(y, s.num_kv_heads, s.key_dim, s.key_dim ** -0.5, s.unit_eps, proj[:, ch : ch + h],

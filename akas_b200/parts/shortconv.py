@@ -26,6 +26,10 @@ class ShortConv(Mixer):
     takes_normed = True
     chain_safe = True
 
+    @classmethod
+    def kernels(cls, spec):
+        return ("short_conv",)
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         if not 2 <= spec.kernel_size <= 16:
