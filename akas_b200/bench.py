@@ -43,10 +43,19 @@ def prefill_flops(runner: ModelRunner, tokens: int, start: int = 0) -> float:
     flops = 2.0 * tokens * p["layers"] + 2.0 * p["head"]
     for entry in runner.model.schedule:
         spec = runner.model.blocks[entry.layer].mixer.spec
-        if getattr(spec, "kind", "") == "attention":
-            # q.k and p.v over (start + i) keys for the i-th token: 4 flops per (query, key, head, channel)
-            pairs = tokens * start + tokens * (tokens + 1) / 2
-            flops += 4.0 * pairs * spec.num_heads * spec.head_dim
+        kind = getattr(spec, "kind", "")
+        if kind == "attention":
+            # q.k and p.v over the keys the i-th token sees (all start + i of them, or a window's worth): 2 flops per
+            # (query, key, head, channel) for each of the two products
+            if spec.window:
+                pairs = sum(min(start + i + 1, spec.window + getattr(spec, "keep_first", 0)) for i in range(tokens))
+            else:
+                pairs = tokens * start + tokens * (tokens + 1) / 2
+            flops += 2.0 * pairs * spec.num_heads * (spec.head_dim + getattr(spec, "value_dim", spec.head_dim))
+        elif kind in ("gated_linear_attention", "gated_delta"):
+            # the matrix state: decay and rank-one update, read-out (and the delta rule's read before the update)
+            per = 6.0 if kind == "gated_delta" else 4.0
+            flops += per * tokens * spec.num_heads * spec.key_dim * spec.value_dim
     return flops
 
 
@@ -62,9 +71,9 @@ def decode_bytes(runner: ModelRunner, contexts: Sequence[int]) -> float:
         if spec is None:
             continue
         if hasattr(spec, "num_kv_heads"):
-            per_token = 2 * spec.num_kv_heads * spec.head_dim * elem
+            per_token = spec.num_kv_heads * (spec.head_dim + (getattr(spec, "v_head_dim", None) or spec.head_dim)) * elem
             for c in contexts:
-                total += per_token * (min(c, spec.window) if spec.window else c)
+                total += per_token * (min(c, spec.window + getattr(spec, "keep_first", 0)) if spec.window else c)
         else:
             total += 2 * len(contexts) * int(np.prod(spec.shape)) * 4
     return total
@@ -336,6 +345,87 @@ def shape_config(name: str) -> dict:
                 block_ffn_dim_multiplier=1.0, tie_embedding=True, max_position_embeddings=128000)
     base.update(SHAPES[name])
     return base
+
+
+# Gigusun at LFM2's layer sizes: the same width, vocabulary and number of layers, mixers and feed-forwards with as many
+# parameters as LFM2's (a short-convolution layer holds 4 C^2 of them, so does a matrix-state mixer with H D = C / 2 and
+# H V = C; PolyNorm's two matrices at the width that gives SwiGLU's three), attention in every third layer.
+def gigusun_shape_config(name: str) -> dict:
+    lfm2 = config_from_shape(name)
+    c, ff3 = lfm2.hidden_size, lfm2.feed_forward_size
+    heads = c // 128
+    ff = -(-(3 * ff3 // 2) // 256) * 256
+    attention = dict(heads=lfm2.num_attention_heads, kv_heads=lfm2.num_key_value_heads, dim=lfm2.head_dim, vdim=lfm2.head_dim,
+                     scale=lfm2.head_dim ** -0.5, softcap=30.0, mask=dict(size=1024, keep_first=4))
+    gla = dict(heads=heads, dim=64, vdim=128, tau=16.0, rank=64)
+    delta = dict(heads=heads, kv_heads=heads // 2, dim=128, vdim=128, conv=4)
+    kinds = {"attention": attention, "gla": gla, "delta": delta}
+    order = ["gla", "delta", "attention"] * 5 + ["gla"]
+    return dict(architecture="Gigusun", width=c, vocab=lfm2.vocab_size, max_positions=8192, norm=dict(eps=1e-5),
+                layers=[dict(type=k, mixer=kinds[k], mlp=dict(ff=ff, kind="dense")) for k in order])
+
+
+def config_from_shape(name: str):
+    from .config import config_from_dict
+
+    return config_from_dict(shape_config(name))
+
+
+def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), steps: int = 64, warmup: int = 4) -> List[dict]:
+    """Gigusun beside LFM2 at equal layer sizes, random weights, bfloat16: milliseconds and tokens a second of a
+    ``prompt``-token prefill and of decode steps at each batch size (captured graphs), and the device time of every
+    kind of operation in an eager prefill and an eager decode step at the first batch size (CUDA events around each
+    call). One row per design."""
+    import tempfile
+
+    from .config import EngineConfig, config_from_dict
+    from .ops import cuda as cuda_ops
+    from .ops.timed import TimedOps
+    from .weights import write_random_model
+
+    rows = []
+    for design, data in (("lfm2", shape_config(shape)), ("gigusun", gigusun_shape_config(shape))):
+        model_config = config_from_dict(data)
+        with tempfile.TemporaryDirectory(prefix="akas-bench-") as folder:
+            write_random_model(folder, model_config, seed=0, dtype="bfloat16")
+            context = prompt + 1024
+            options = dict(dtype="bfloat16", max_requests=max(batches), context=context, max_tokens=max(batches) * context,
+                           page_size=64, prefill_chunk=prompt, prefill_token_budget=max(8192, prompt))
+            runner = ModelRunner(folder, EngineConfig(**options))
+            vocab = runner.vocab_size
+            text = synthetic_prompts(1, prompt, vocab)[0]
+            pre_ms = measure_prefill(runner, text, repeats=5, warmup=3)
+            row = dict(design=design, shape=shape, parameters=sum(matrix_params(runner).values()),
+                       prefill=dict(tokens=prompt, ms=round(pre_ms, 3), tokens_per_s=round(prompt / pre_ms * 1e3, 1),
+                                    tflops=round(prefill_flops(runner, prompt) / pre_ms / 1e9, 1)), decode={})
+            for batch in batches:
+                run = measure_decode(runner, batch, prompt, steps, warmup, repeats=3)
+                row["decode"][str(batch)] = dict(ms_per_step=round(run["ms_per_step"], 4), tokens_per_s=round(run["tokens_per_s"], 1),
+                                                 gb_per_s=round(run["bytes"] / run["ms_per_step"] / 1e6, 1),
+                                                 kernels=runner.kernels_per_decode_step.get(runner.decode_capacity(batch), 0))
+            del runner
+            torch.cuda.empty_cache()
+            timed = TimedOps(cuda_ops)
+            eager = ModelRunner(folder, EngineConfig(**dict(options, cuda_graphs=False)), ops=timed)
+            for _ in range(2):
+                eager.step([StepEntry("p", text, (prompt - 1,))])
+                eager.release("p")
+            timed.clear()
+            eager.step([StepEntry("p", text, (prompt - 1,))])
+            row["prefill_ops"] = [dict(op=r["op"], calls=r["calls"], ms=round(r["ms"], 4)) for r in timed.table()]
+            eager.release("p")
+            batch = batches[0]
+            ids = fill_requests(eager, synthetic_prompts(batch, prompt, vocab), prompt)
+            step = [StepEntry(rid, (1,), (0,)) for rid in ids]
+            for _ in range(3):
+                eager.step(step)
+            timed.clear()
+            eager.step(step)
+            row["decode_ops"] = [dict(op=r["op"], calls=r["calls"], ms=round(r["ms"], 4)) for r in timed.table()]
+            del eager
+            torch.cuda.empty_cache()
+        rows.append(row)
+    return rows
 
 
 def _random_engine(shape: str, **options):

@@ -58,11 +58,34 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ q, long long ldq, con
   }
 }
 
+// Scores of one key row against `heads` query rows in shared memory: the row is read once, 16 bytes at a time where
+// its size allows, and every head's sum is one ascending chain of fused multiply-adds.
 template <typename T>
-__device__ __forceinline__ float dot_row(const T* __restrict__ krow, const float* __restrict__ qs, int D) {
-  float acc = 0.f;
-  for (int d = 0; d < D; ++d) acc = fmaf(qs[d], to_f32(krow[d]), acc);
-  return acc;
+__device__ __forceinline__ void dot_rows(const T* __restrict__ krow, const float* __restrict__ qs, int D, int heads,
+                                         float (&acc)[kMaxGroup]) {
+  constexpr int N = Vec<T>::N;
+#pragma unroll
+  for (int a = 0; a < kMaxGroup; ++a) acc[a] = 0.f;
+  int d = 0;
+  if ((D * (int)sizeof(T)) % 16 == 0) {
+    for (; d + N <= D; d += N) {
+      float kv[N];
+      load_vec(krow + d, kv);
+#pragma unroll
+      for (int a = 0; a < kMaxGroup; ++a) {
+        if (a < heads) {
+#pragma unroll
+          for (int e = 0; e < N; ++e) acc[a] = fmaf(qs[a * D + d + e], kv[e], acc[a]);
+        }
+      }
+    }
+  }
+  for (; d < D; ++d) {
+    const float kv = to_f32(krow[d]);
+#pragma unroll
+    for (int a = 0; a < kMaxGroup; ++a)
+      if (a < heads) acc[a] = fmaf(qs[a * D + d], kv, acc[a]);
+  }
 }
 
 // One block of kTile threads per (token, key/value head). In a tile, thread t owns key t: it computes the scores
@@ -74,8 +97,8 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_of_token,
                          const int* __restrict__ positions, T* __restrict__ out, float scale, int window, int keep_first,
                          float cap, const float* __restrict__ r1, const float* __restrict__ r2, int sink,
-                         const TG* __restrict__ gate, long long ldg, int page_size, int H, int G, int D, int V) {
-  extern __shared__ float smem[];
+                         const TG* __restrict__ gate, long long ldg, int page_size, int H, int G, int D, int V, int row_words) {
+  extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x, g = blockIdx.y;
   const int req = seq_of_token[n];
   if (req < 0) return;
@@ -93,6 +116,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
     float* pw = qs + kMaxGroup * D;          // [heads][kTile] weights of the tile
     float* red = pw + kMaxGroup * kTile;     // [kMaxGroup][4] maxima / sums of the warps
     float* stat = red + kMaxGroup * 4;       // [kMaxGroup][2]: running maximum, correction of this tile
+    long long* rowbase = reinterpret_cast<long long*>(smem + row_words);  // [kTile] row of each key of the tile in the pools
     __syncthreads();
     for (int i = tid; i < heads * D; i += kTile)
       qs[i] = to_f32(q[((size_t)n * H + (size_t)g * group + h0) * D + i]);
@@ -100,7 +124,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
 #pragma unroll
     for (int a = 0; a < kMaxGroup; ++a) { m_run[a] = sink ? 0.f : -INFINITY; l_run[a] = sink ? 1.f : 0.f; }
     // running sums of value channel c = tid + kTile * i for every head: kept in shared memory (any V), thread-private
-    float* acc = stat + kMaxGroup * 2;  // [heads][Vp], Vp = V rounded up to kTile
+    float* acc = stat + kMaxGroup * 2;  // [kMaxGroup][Vp], Vp = V rounded up to kTile
     const int Vp = (V + kTile - 1) / kTile * kTile;
     for (int i = tid; i < heads * Vp; i += kTile) acc[i] = 0.f;
     __syncthreads();
@@ -115,12 +139,14 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
         float sc[kMaxGroup];
         if (seen) {
           const int page = table[key / page_size];
-          const T* krow = k_pool + (((size_t)page * G + g) * page_size + key % page_size) * D;
+          const long long base = ((long long)page * G + g) * page_size + key % page_size;
+          rowbase[tid] = base;
           const float dist = (float)(pos - key);
+          dot_rows(k_pool + (size_t)base * D, qs, D, heads, sc);
 #pragma unroll
           for (int a = 0; a < kMaxGroup; ++a) {
             if (a < heads) {
-              float s = dot_row(krow, qs + a * D, D) * scale;
+              float s = sc[a] * scale;
               if (cap > 0.f) s = cap * tanhf(s / cap);
               if (r1 != nullptr) {
                 const int h = g * group + h0 + a;
@@ -169,10 +195,9 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
           float add[kMaxGroup];
 #pragma unroll
           for (int a = 0; a < kMaxGroup; ++a) add[a] = 0.f;
-          for (int t = begin; t < count; ++t) {
-            const int kk = t0 + t;
-            const int page = table[kk / page_size];
-            const float vv = to_f32(v_pool[(((size_t)page * G + g) * page_size + kk % page_size) * V + c]);
+#pragma unroll 8
+          for (int t = begin; t < count; ++t) {  // (the rows' places were found with the scores: these loads do not wait on one another)
+            const float vv = to_f32(v_pool[(size_t)rowbase[t] * V + c]);
 #pragma unroll
             for (int a = 0; a < kMaxGroup; ++a)
               if (a < heads) add[a] = fmaf(pw[a * kTile + t], vv, add[a]);
@@ -226,7 +251,8 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
                           float cap, const float* r1, const float* r2, int sink, const void* gate, long long ldg,
                           int page_size, int N, int H, int G, int D, int V, cudaStream_t stream) {
   const int Vp = (V + kTile - 1) / kTile * kTile;
-  const size_t smem = sizeof(float) * ((size_t)kMaxGroup * D + kMaxGroup * kTile + kMaxGroup * 4 + kMaxGroup * 2 + (size_t)kMaxGroup * Vp);
+  const int row_words = (kMaxGroup * D + kMaxGroup * kTile + kMaxGroup * 4 + kMaxGroup * 2 + kMaxGroup * Vp + 1) / 2 * 2;
+  const size_t smem = sizeof(float) * (size_t)row_words + sizeof(long long) * kTile;
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   static size_t allowed[64] = {};
   int device = 0;
@@ -238,7 +264,7 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
   }
   attention_general_kernel<T, TG><<<dim3(N, G), kTile, smem, stream>>>(
       (const T*)q, (const T*)k_pool, (const T*)v_pool, block_table, max_blocks, seq_of_token, positions, (T*)out, scale, window,
-      keep_first, cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V);
+      keep_first, cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words);
   return launch_status();
 }
 

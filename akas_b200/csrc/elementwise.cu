@@ -259,39 +259,81 @@ AKAS_API int akas_add_rows(float* h, const void* table, const int* index, int N,
   return launch_status();
 }
 
-// PolyNorm on float32 rows: out = a N(z) + b N(z^2) + c N(z^3) + e with N(x) = x / sqrt(mean(x^2) + eps) over the row
-// and the powers taken element by element; coeffs = (a, b, c, e). One block per row, float32 sums.
-template <typename TO>
-__global__ void polynorm_kernel(const float* __restrict__ z, const float* __restrict__ coeffs, float eps,
+// PolyNorm of rows: out = a N(z) + b N(z^2) + c N(z^3) + e with N(x) = x / sqrt(mean(x^2) + eps) over the row and
+// the powers taken element by element; coeffs = (a, b, c, e). One block per row; powers and sums are float32. VEC: the
+// row's width is a multiple of 8 and rows start on 16 bytes, so 8 elements move at a time.
+template <typename TI, typename TO, bool VEC>
+__global__ void polynorm_kernel(const TI* __restrict__ z, const float* __restrict__ coeffs, float eps,
                                 TO* __restrict__ out, int F) {
-  __shared__ float scratch[32];
-  const float* row = z + (size_t)blockIdx.x * F;
+  __shared__ float scratch[3][32];
+  const TI* row = z + (size_t)blockIdx.x * F;
   float s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  for (int c = threadIdx.x; c < F; c += blockDim.x) {
-    const float x = row[c], x2 = x * x, x3 = x2 * x;
-    s1 = fmaf(x, x, s1);
-    s2 = fmaf(x2, x2, s2);
-    s3 = fmaf(x3, x3, s3);
+  if (VEC) {
+    for (int c = threadIdx.x * 8; c < F; c += blockDim.x * 8) {
+      float x[8];
+      load8(row + c, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float x2 = x[e] * x[e], x3 = x2 * x[e];
+        s1 = fmaf(x[e], x[e], s1);
+        s2 = fmaf(x2, x2, s2);
+        s3 = fmaf(x3, x3, s3);
+      }
+    }
+  } else {
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+      const float x = to_f32(row[c]), x2 = x * x, x3 = x2 * x;
+      s1 = fmaf(x, x, s1);
+      s2 = fmaf(x2, x2, s2);
+      s3 = fmaf(x3, x3, s3);
+    }
   }
-  s1 = block_sum(s1, scratch);
-  s2 = block_sum(s2, scratch);
-  s3 = block_sum(s3, scratch);
+  // the three sums meet together: one pair of barriers instead of three
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  s1 = warp_sum(s1); s2 = warp_sum(s2); s3 = warp_sum(s3);
+  if (lane == 0) { scratch[0][warp] = s1; scratch[1][warp] = s2; scratch[2][warp] = s3; }
+  __syncthreads();
+  s1 = warp_sum(lane < warps ? scratch[0][lane] : 0.f);
+  s2 = warp_sum(lane < warps ? scratch[1][lane] : 0.f);
+  s3 = warp_sum(lane < warps ? scratch[2][lane] : 0.f);
   const float i1 = coeffs[0] / sqrtf(s1 / (float)F + eps);
   const float i2 = coeffs[1] / sqrtf(s2 / (float)F + eps);
   const float i3 = coeffs[2] / sqrtf(s3 / (float)F + eps);
-  const float e = coeffs[3];
+  const float e0 = coeffs[3];
   TO* dst = out + (size_t)blockIdx.x * F;
-  for (int c = threadIdx.x; c < F; c += blockDim.x) {
-    const float x = row[c], x2 = x * x;
-    dst[c] = from_f32<TO>(fmaf(x, i1, fmaf(x2, i2, fmaf(x2 * x, i3, e))));
+  if (VEC) {
+    for (int c = threadIdx.x * 8; c < F; c += blockDim.x * 8) {
+      float x[8], y[8];
+      load8(row + c, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float x2 = x[e] * x[e];
+        y[e] = fmaf(x[e], i1, fmaf(x2, i2, fmaf(x2 * x[e], i3, e0)));
+      }
+      store8(dst + c, y);
+    }
+  } else {
+    for (int c = threadIdx.x; c < F; c += blockDim.x) {
+      const float x = to_f32(row[c]), x2 = x * x;
+      dst[c] = from_f32<TO>(fmaf(x, i1, fmaf(x2, i2, fmaf(x2 * x, i3, e0))));
+    }
   }
 }
 
-AKAS_API int akas_polynorm(const float* z, const float* coeffs, float eps, void* out, int N, int F, int out_dtype,
-                           cudaStream_t stream) {
+AKAS_API int akas_polynorm(const void* z, const float* coeffs, float eps, void* out, int N, int F, int in_dtype,
+                           int out_dtype, cudaStream_t stream) {
   if (N <= 0) return 0;
-  const int threads = F >= 2048 ? 512 : 256;
-  if (out_dtype == AKAS_F32) polynorm_kernel<float><<<N, threads, 0, stream>>>(z, coeffs, eps, (float*)out, F);
-  else polynorm_kernel<bf16><<<N, threads, 0, stream>>>(z, coeffs, eps, (bf16*)out, F);
+  const int threads = F >= 4096 ? 512 : F >= 1024 ? 256 : 128;
+  const bool vec = F % 8 == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0;
+#define AKAS_POLY(TI, TO)                                                                                              \
+  {                                                                                                                    \
+    if (vec) polynorm_kernel<TI, TO, true><<<N, threads, 0, stream>>>((const TI*)z, coeffs, eps, (TO*)out, F);         \
+    else polynorm_kernel<TI, TO, false><<<N, threads, 0, stream>>>((const TI*)z, coeffs, eps, (TO*)out, F);            \
+  }
+  if (in_dtype == AKAS_F32 && out_dtype == AKAS_F32) AKAS_POLY(float, float)
+  else if (in_dtype == AKAS_F32) AKAS_POLY(float, bf16)
+  else if (out_dtype == AKAS_F32) AKAS_POLY(bf16, float)
+  else AKAS_POLY(bf16, bf16)
+#undef AKAS_POLY
   return launch_status();
 }

@@ -21,8 +21,9 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-
 
 // ------------------------------------------------------------------------------------------------ decay gates
 //
-// out[n, o] = sigmoid(z)^(1 / tau), z = sum_r low[n, r] * w[o, r] + bias[o]: the up projection of a low-rank pair in
-// float32 (one ascending chain of fused multiply-adds per output), then exp(log sigmoid(z) / tau).
+// out[n, o] = sigmoid(z)^(1 / tau), z = sum_r low[n, r] * wt[r, o] + bias[o]: the up projection of a low-rank pair in
+// float32 (one ascending chain of fused multiply-adds per output), then exp(log sigmoid(z) / tau). The matrix comes
+// transposed, [R, O], so that the threads of a warp read neighbouring words.
 constexpr int kGateTokens = 8;
 
 template <typename T>
@@ -40,9 +41,8 @@ __global__ void decay_gates_kernel(const T* __restrict__ low, long long ld, cons
     float acc[kGateTokens];
 #pragma unroll
     for (int t = 0; t < kGateTokens; ++t) acc[t] = 0.f;
-    const float* wr = w + (size_t)o * R;
     for (int r = 0; r < R; ++r) {
-      const float wv = wr[r];
+      const float wv = w[(size_t)r * O + o];
 #pragma unroll
       for (int t = 0; t < kGateTokens; ++t) acc[t] = fmaf(rows[t * R + r], wv, acc[t]);
     }
@@ -55,7 +55,7 @@ __global__ void decay_gates_kernel(const T* __restrict__ low, long long ld, cons
 
 // ------------------------------------------------------------------------------------------------ the recurrences
 //
-// One block per (head, request, tile of value channels). A thread owns R consecutive key channels of one value
+// One block of TH threads per (head, request, tile of value channels). A thread owns R consecutive key channels of one value
 // channel j: s[r] = S[ks * R + r][j]; the KS threads of a value channel are neighbouring lanes of a warp and add
 // their partial sums by shuffles. The step's tokens come through shared memory in chunks of CH (fewer where rows are long).
 //
@@ -69,14 +69,14 @@ template <int KS> __device__ __forceinline__ float group_sum(float v) {
   return v;
 }
 
-template <typename T, int R, int KS, int CH, bool DELTA>
-__global__ void __launch_bounds__(256)
+template <typename T, int R, int KS, int CH, int TH, bool DELTA>
+__global__ void __launch_bounds__(TH)
 scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk, const T* __restrict__ v,
             long long ldv, const float* __restrict__ decay /* GLA: alpha [N, H * D]; DELTA: g [N, H] */,
             const float* __restrict__ beta /* DELTA: [N, H] */, float* __restrict__ state, long long slot_stride,
             const int* __restrict__ cu_seqlens, const int* __restrict__ slots, float* __restrict__ out, int H, int rep,
             int D, int V, float q_scale, int write) {
-  constexpr int VT = 256 / KS;          // value channels of a block
+  constexpr int VT = TH / KS;           // value channels of a block
   constexpr int ROW = KS * (R + kPad);  // floats of a padded shared row of key channels
   __shared__ __align__(16) float sq[CH][ROW];
   __shared__ __align__(16) float sk[CH][ROW];
@@ -108,43 +108,74 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
     }
   }
 
+  // A chunk's inputs are fetched into registers while the chunk before it is computed, and put into shared memory
+  // when that is done: the recurrence never waits for global memory except at its first chunk.
+  constexpr int NQ = (CH * KS * R + TH - 1) / TH, NV = (CH * VT + TH - 1) / TH;
+  float rq[NQ], rk[NQ], ra[DELTA ? 1 : NQ], rv[NV], rg = 0.f, rb = 0.f;
+  auto fetch = [&](int c0) {
+    const int count = min(CH, t_end - c0);
+#pragma unroll
+    for (int u = 0; u < NQ; ++u) {
+      const int i = threadIdx.x + u * TH;
+      const int t = i / (KS * R), kk = i % (KS * R);
+      const bool in = t < count && kk < D;
+      const size_t n = (size_t)(c0 + t);
+      rq[u] = in ? to_f32(q[n * ldq + (size_t)hk * D + kk]) * q_scale : 0.f;
+      rk[u] = in ? to_f32(k[n * ldk + (size_t)hk * D + kk]) : 0.f;
+      if (!DELTA) ra[u] = in ? decay[n * ((size_t)H * D) + (size_t)h * D + kk] : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      const int i = threadIdx.x + u * TH;
+      const int t = i / VT, col = blockIdx.z * VT + i % VT;
+      rv[u] = t < count && col < V ? to_f32(v[(size_t)(c0 + t) * ldv + (size_t)h * V + col]) : 0.f;
+    }
+    if (DELTA && threadIdx.x < count) {
+      rg = decay[(size_t)(c0 + threadIdx.x) * H + h];
+      rb = beta[(size_t)(c0 + threadIdx.x) * H + h];
+    }
+  };
+  fetch(t_begin);
   for (int c0 = t_begin; c0 < t_end; c0 += CH) {
     const int count = min(CH, t_end - c0);
     __syncthreads();  // the chunk before has been read
-    for (int i = threadIdx.x; i < count * KS * R; i += 256) {
-      const int t = i / (KS * R), kk = i % (KS * R);
-      const int at = kk + (kk / R) * kPad;
-      const bool in = kk < D;
-      const size_t n = (size_t)(c0 + t);
-      sq[t][at] = in ? to_f32(q[n * ldq + (size_t)hk * D + kk]) * q_scale : 0.f;
-      sk[t][at] = in ? to_f32(k[n * ldk + (size_t)hk * D + kk]) : 0.f;
-      if (!DELTA) sa[t][at] = in ? decay[n * ((size_t)H * D) + (size_t)h * D + kk] : 0.f;
+#pragma unroll
+    for (int u = 0; u < NQ; ++u) {
+      const int i = threadIdx.x + u * TH;
+      if (i < CH * KS * R) {
+        const int t = i / (KS * R), kk = i % (KS * R);
+        const int at = kk + (kk / R) * kPad;
+        sq[t][at] = rq[u];
+        sk[t][at] = rk[u];
+        if (!DELTA) sa[t][at] = ra[u];
+      }
     }
-    for (int i = threadIdx.x; i < count * VT; i += 256) {
-      const int t = i / VT, jj = i % VT;
-      const int col = blockIdx.z * VT + jj;
-      sv[t][jj] = col < V ? to_f32(v[(size_t)(c0 + t) * ldv + (size_t)h * V + col]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      const int i = threadIdx.x + u * TH;
+      if (i < CH * VT) sv[i / VT][i % VT] = rv[u];
     }
-    if (DELTA && threadIdx.x < count) {
-      sg[threadIdx.x] = decay[(size_t)(c0 + threadIdx.x) * H + h];
-      sb[threadIdx.x] = beta[(size_t)(c0 + threadIdx.x) * H + h];
+    if (DELTA && threadIdx.x < CH) {
+      sg[threadIdx.x] = rg;
+      sb[threadIdx.x] = rb;
     }
     __syncthreads();
+    if (c0 + CH < t_end) fetch(c0 + CH);
     for (int t = 0; t < count; ++t) {
       const float* qr = &sq[t][ks * (R + kPad)];
       const float* kr = &sk[t][ks * (R + kPad)];
       const float vj = sv[t][jl];
-      float acc = 0.f;
+      float acc = 0.f, acc2 = 0.f;  // two chains of sums, added before the lanes meet: always in this order
       if (DELTA) {
         const float g = sg[t];
-        float pk = 0.f;
+        float pk = 0.f, pk2 = 0.f;
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
           const float4 kv = *reinterpret_cast<const float4*>(kr + r);
           s[r] *= g; s[r + 1] *= g; s[r + 2] *= g; s[r + 3] *= g;
-          pk = fmaf(s[r], kv.x, pk); pk = fmaf(s[r + 1], kv.y, pk); pk = fmaf(s[r + 2], kv.z, pk); pk = fmaf(s[r + 3], kv.w, pk);
+          pk = fmaf(s[r], kv.x, pk); pk2 = fmaf(s[r + 1], kv.y, pk2); pk = fmaf(s[r + 2], kv.z, pk); pk2 = fmaf(s[r + 3], kv.w, pk2);
         }
-        pk = group_sum<KS>(pk);
+        pk = group_sum<KS>(pk + pk2);
         const float u = sb[t] * (vj - pk);
 #pragma unroll
         for (int r = 0; r < R; r += 4) {
@@ -152,7 +183,7 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
           const float4 qv = *reinterpret_cast<const float4*>(qr + r);
           s[r] = fmaf(kv.x, u, s[r]); s[r + 1] = fmaf(kv.y, u, s[r + 1]);
           s[r + 2] = fmaf(kv.z, u, s[r + 2]); s[r + 3] = fmaf(kv.w, u, s[r + 3]);
-          acc = fmaf(s[r], qv.x, acc); acc = fmaf(s[r + 1], qv.y, acc); acc = fmaf(s[r + 2], qv.z, acc); acc = fmaf(s[r + 3], qv.w, acc);
+          acc = fmaf(s[r], qv.x, acc); acc2 = fmaf(s[r + 1], qv.y, acc2); acc = fmaf(s[r + 2], qv.z, acc); acc2 = fmaf(s[r + 3], qv.w, acc2);
         }
       } else {
         const float* ar = &sa[t][ks * (R + kPad)];
@@ -163,10 +194,10 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
           const float4 av = *reinterpret_cast<const float4*>(ar + r);
           s[r] = fmaf(av.x, s[r], kv.x * vj); s[r + 1] = fmaf(av.y, s[r + 1], kv.y * vj);
           s[r + 2] = fmaf(av.z, s[r + 2], kv.z * vj); s[r + 3] = fmaf(av.w, s[r + 3], kv.w * vj);
-          acc = fmaf(s[r], qv.x, acc); acc = fmaf(s[r + 1], qv.y, acc); acc = fmaf(s[r + 2], qv.z, acc); acc = fmaf(s[r + 3], qv.w, acc);
+          acc = fmaf(s[r], qv.x, acc); acc2 = fmaf(s[r + 1], qv.y, acc2); acc = fmaf(s[r + 2], qv.z, acc); acc2 = fmaf(s[r + 3], qv.w, acc2);
         }
       }
-      acc = group_sum<KS>(acc);
+      acc = group_sum<KS>(acc + acc2);
       if (ks == 0 && live) out[(size_t)(c0 + t) * ((size_t)H * V) + (size_t)h * V + j] = acc;
     }
   }
@@ -187,14 +218,19 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
 template <typename T, bool DELTA>
 int launch_scan(const T* q, long long ldq, const T* k, long long ldk, const T* v, long long ldv, const float* decay,
                 const float* beta, float* state, long long slot_stride, const int* cu_seqlens, const int* slots, float* out,
-                int requests, int H, int rep, int D, int V, float q_scale, int write, cudaStream_t stream) {
+                int tokens, int requests, int H, int rep, int D, int V, float q_scale, int write, cudaStream_t stream) {
   if (requests <= 0 || H <= 0) return 0;
   if (D > 1024) return (int)cudaErrorInvalidValue;
+  // (Blocks of 64 threads, which spread a head's value channels over four times as many SMs when a step holds few
+  // long portions, were measured and dropped: a token's cost is the latency of its chain of shared-memory reads, sums
+  // and shuffles, which fewer warps per SM hide less well. 2,048 tokens, 16 heads of 128 x 128: 0.94 against 0.75 ms.)
+  (void)tokens;
 #define AKAS_SCAN(R, KS, CH)                                                                                              \
   {                                                                                                                       \
     const dim3 grid(H, requests, (V + 256 / KS - 1) / (256 / KS));                                                        \
-    scan_kernel<T, R, KS, CH, DELTA><<<grid, 256, 0, stream>>>(q, ldq, k, ldk, v, ldv, decay, beta, state, slot_stride,   \
-                                                           cu_seqlens, slots, out, H, rep, D, V, q_scale, write);         \
+    scan_kernel<T, R, KS, CH, 256, DELTA><<<grid, 256, 0, stream>>>(q, ldq, k, ldk, v, ldv, decay, beta, state,           \
+                                                                    slot_stride, cu_seqlens, slots, out, H, rep, D, V,    \
+                                                                    q_scale, write);                                      \
     return launch_status();                                                                                               \
   }
   if (D <= 8) AKAS_SCAN(8, 1, 16)
@@ -319,22 +355,22 @@ AKAS_API int akas_decay_gates(const void* low, long long ld, const float* w, con
 
 AKAS_API int akas_gla_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
                            const float* alpha, float* state, long long slot_stride, const int* cu_seqlens, const int* slots,
-                           float* out, int requests, int H, int D, int V, float q_scale, int write, int dtype,
+                           float* out, int tokens, int requests, int H, int D, int V, float q_scale, int write, int dtype,
                            cudaStream_t stream) {
   if (dtype == AKAS_F32)
     return launch_scan<float, false>((const float*)q, ldq, (const float*)k, ldk, (const float*)v, ldv, alpha, nullptr, state,
-                                     slot_stride, cu_seqlens, slots, out, requests, H, 1, D, V, q_scale, write, stream);
+                                     slot_stride, cu_seqlens, slots, out, tokens, requests, H, 1, D, V, q_scale, write, stream);
   return launch_scan<bf16, false>((const bf16*)q, ldq, (const bf16*)k, ldk, (const bf16*)v, ldv, alpha, nullptr, state,
-                                  slot_stride, cu_seqlens, slots, out, requests, H, 1, D, V, q_scale, write, stream);
+                                  slot_stride, cu_seqlens, slots, out, tokens, requests, H, 1, D, V, q_scale, write, stream);
 }
 
 AKAS_API int akas_delta_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
                              const float* beta, const float* g, float* state, long long slot_stride, const int* cu_seqlens,
-                             const int* slots, float* out, int requests, int H, int G, int D, int V, int write,
+                             const int* slots, float* out, int tokens, int requests, int H, int G, int D, int V, int write,
                              cudaStream_t stream) {
   if (G <= 0 || H % G) return (int)cudaErrorInvalidValue;
-  return launch_scan<float, true>(q, ldq, k, ldk, v, ldv, g, beta, state, slot_stride, cu_seqlens, slots, out, requests, H,
-                                  H / G, D, V, 1.f, write, stream);
+  return launch_scan<float, true>(q, ldq, k, ldk, v, ldv, g, beta, state, slot_stride, cu_seqlens, slots, out, tokens,
+                                  requests, H, H / G, D, V, 1.f, write, stream);
 }
 
 AKAS_API int akas_causal_conv_silu(const void* x, long long ldx, const float* taps, float* state, long long slot_stride,

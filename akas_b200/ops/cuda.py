@@ -37,14 +37,14 @@ _SIGNATURES = {
         "akas_add_bias": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_scale_cap": [c_void_p, c_float, c_float, c_longlong, c_void_p],
         "akas_add_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-        "akas_polynorm": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_polynorm": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "recurrent": {
         "akas_decay_gates": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "akas_gla_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
-                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
         "akas_delta_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
-                            c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "akas_causal_conv_silu": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "akas_delta_prep": [c_void_p, c_longlong, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_void_p, c_longlong,
@@ -59,6 +59,12 @@ _SIGNATURES = {
         "akas_attention_general": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                    c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
                                    c_int, c_int, c_int, c_void_p],
+    },
+    "attention_general_tc": {
+        "akas_attention_general_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
+                                      c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_attention_general_tc_takes": [c_int, c_int],
     },
     "conv": {
         "akas_short_conv": [c_void_p] * 8 + [c_int] * 6 + [c_void_p],
@@ -187,7 +193,7 @@ _PART_FILES = {
     "attention": lambda dtype: ["rope", "attention"] + (["attention_prefill", "attention_prefill_tc", "attention_decode"]
                                                         if dtype == torch.bfloat16 else []),
     "short_conv": lambda dtype: ["conv"],
-    "attention_general": lambda dtype: ["attention_general"],
+    "attention_general": lambda dtype: ["attention_general"] + (["attention_general_tc"] if dtype == torch.bfloat16 else []),
     "recurrent": lambda dtype: ["recurrent"],
 }
 
@@ -477,6 +483,11 @@ def linear(x, w, out_dtype=None, residual=None):
         return out
     if x.dtype != torch.bfloat16:
         raise TypeError(f"linear takes float32 or bfloat16, got {x.dtype}")
+    if k % 8 and _pad_inner:
+        # The tensor-core kernels take inner sizes that are multiples of 8 (16 bytes of bfloat16): both operands get
+        # columns of zeros up to the next one. The weights are padded once and kept.
+        x, w = _padded_inner(x, False), _padded_inner(w, True)
+        k = x.shape[1]
     target = out_dtype or torch.bfloat16
     mode = _OUT_ACC if residual is not None else _OUT_F32 if target == torch.float32 else _OUT_BF16
     if _chain_takes(n, o, k, 0, mode):
@@ -509,6 +520,21 @@ def linear(x, w, out_dtype=None, residual=None):
     ws = _workspace(x.device)
     _check(_fn("gemm_bf16", "akas_gemm_bf16")(_ptr(x), _ptr(w), _ptr(out), n, o, k, out_f32, acc, _ptr(ws),
                                              ws.numel(), _stream()), f"bfloat16 product [{n}x{k}] x [{o}x{k}]^T")
+    return out
+
+
+_pad_inner = True  # False: an inner size that is no multiple of 8 is refused, as the kernels themselves refuse it
+_padded_weights = {}
+
+
+def _padded_inner(t, keep: bool):
+    """``t`` [rows, K] with zero columns up to the next multiple of 8; for weights (``keep``) made once per tensor."""
+    key = (t.data_ptr(), tuple(t.shape), t.device)
+    if keep and key in _padded_weights:
+        return _padded_weights[key][1]
+    out = torch.nn.functional.pad(t, (0, -t.shape[1] % 8)).contiguous()
+    if keep:
+        _padded_weights[key] = (t, out)  # the original is held too, so that its address is not handed out again
     return out
 
 
@@ -1099,12 +1125,12 @@ def add_rows(h, table, index):
 
 @_flushes
 def polynorm(z, coeffs, eps, out_dtype):
-    """a N(z) + b N(z^2) + c N(z^3) + e per row of float32 z [N, F]; coeffs = (a, b, c, e) float32."""
+    """a N(z) + b N(z^2) + c N(z^3) + e per row of z [N, F]; coeffs = (a, b, c, e) float32. Powers and sums are float32."""
     n, f = z.shape
-    if z.dtype != torch.float32 or coeffs.dtype != torch.float32 or coeffs.numel() != 4:
-        raise ValueError("polynorm takes float32 z [N, F] and four float32 coefficients")
+    if coeffs.dtype != torch.float32 or coeffs.numel() != 4:
+        raise ValueError("polynorm takes z [N, F] and four float32 coefficients")
     out = torch.empty((n, f), dtype=out_dtype, device=z.device)
-    _check(_fn("elementwise", "akas_polynorm")(_ptr(_dense(z, "z")), _ptr(coeffs), float(eps), _ptr(out), n, f,
+    _check(_fn("elementwise", "akas_polynorm")(_ptr(_dense(z, "z")), _ptr(coeffs), float(eps), _ptr(out), n, f, _code(z),
                                               _CODE[out_dtype], _stream()), "polynorm")
     return out
 
@@ -1128,12 +1154,12 @@ def _slot_rows(state: torch.Tensor, what: str):
 
 @_flushes
 def decay_gates(low, w_up, bias, tau):
-    """sigmoid(low . w_up^T + bias)^(1 / tau), float32 [N, O], for low [N, R] (a slice of a product's result) and
-    float32 w_up [O, R]."""
+    """sigmoid(low . w_up + bias)^(1 / tau), float32 [N, O], for low [N, R] (a slice of a product's result) and
+    float32 w_up [R, O] (the up matrix of the low-rank pair, transposed)."""
     n, r = low.shape
-    o = w_up.shape[0]
-    if w_up.dtype != torch.float32 or bias.dtype != torch.float32 or w_up.shape[1] != r:
-        raise ValueError("decay_gates takes a float32 matrix [O, R] and bias [O]")
+    o = w_up.shape[1]
+    if w_up.dtype != torch.float32 or bias.dtype != torch.float32 or w_up.shape[0] != r:
+        raise ValueError("decay_gates takes a float32 matrix [R, O] and bias [O]")
     ptr, ld = _rows(low, "low")
     out = torch.empty((n, o), dtype=torch.float32, device=low.device)
     _check(_fn("recurrent", "akas_decay_gates")(ptr, ld, _ptr(_dense(w_up, "w_up")), _ptr(bias), _ptr(out), n, o, r, float(tau),
@@ -1150,7 +1176,7 @@ def gla_scan(q, k, v, alpha, state, cu_seqlens, slots, heads, dim, vdim, q_scale
     sp, stride = _slot_rows(state, "state")
     out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
     _check(_fn("recurrent", "akas_gla_scan")(qp, ldq, kp, ldk, vp, ldv, _ptr(alpha), sp, stride, _ptr(cu_seqlens), _ptr(slots),
-                                            _ptr(out), slots.numel(), heads, dim, vdim, float(q_scale), int(bool(write)),
+                                            _ptr(out), n, slots.numel(), heads, dim, vdim, float(q_scale), int(bool(write)),
                                             _code(q), _stream()), "gla_scan")
     return out
 
@@ -1195,7 +1221,7 @@ def delta_scan(q, k, v, beta, g, state, cu_seqlens, slots, heads, kv_heads, dim,
     sp, stride = _slot_rows(state, "state")
     out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
     _check(_fn("recurrent", "akas_delta_scan")(qp, ldq, kp, ldk, vp, ldv, _ptr(beta), _ptr(g), sp, stride, _ptr(cu_seqlens),
-                                              _ptr(slots), _ptr(out), slots.numel(), heads, kv_heads, dim, vdim,
+                                              _ptr(slots), _ptr(out), n, slots.numel(), heads, kv_heads, dim, vdim,
                                               int(bool(write)), _stream()), "delta_scan")
     return out
 
@@ -1230,6 +1256,14 @@ def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, 
     return out
 
 
+# Which kernel runs the general attention over prompt portions in bfloat16: "mma" (default), the tensor-core kernel
+# (csrc/attention_general_tc.cu) for requests that bring more than one token, the single tokens at the step's front on
+# the kernel for any sizes; "plain": that kernel for everything.
+general_attention = os.environ.get("AKAS_B200_GENERAL_ATTENTION", "mma")
+if general_attention not in ("mma", "plain"):
+    raise ValueError(f"AKAS_B200_GENERAL_ATTENTION must be mma or plain, got {general_attention!r}")
+
+
 @_flushes
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
                       r1, r2, sink, gate, page_size, ctx=None):
@@ -1241,10 +1275,32 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
         raise TypeError("attention_general: q, the pages and the gate must have one dtype")
     gp, ldg = _rows(gate, "gate") if gate is not None else (None, 0)
     out = torch.empty((n, heads * vd), dtype=q.dtype, device=q.device)
-    _check(_fn("attention_general", "akas_attention_general")(
-        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions),
-        _ptr(out), float(scale), int(window or 0), int(keep_first or 0), float(softcap or 0.0), _ptr(r1), _ptr(r2),
-        int(bool(sink)), gp, ldg, page_size, n, heads, kh, d, vd, _code(q), _stream()), "attention_general")
+    options = (float(scale), int(window or 0), int(keep_first or 0), float(softcap or 0.0), _ptr(r1), _ptr(r2),
+               int(bool(sink)), gp, ldg, page_size)
+    singles = n  # tokens at the front that are left to the kernel for any sizes
+    lens = getattr(ctx, "query_lens", ()) if ctx is not None else ()
+    if (general_attention == "mma" and q.dtype == torch.bfloat16 and lens
+            and _fn("attention_general_tc", "akas_attention_general_tc_takes")(d, vd)):
+        # The single tokens at the step's front (decoding requests) as one launch whose blocks hold the query heads of
+        # a key/value head; then the requests from the first that brings more, as 64-query tiles. The kernel finds its
+        # tiles from cu_seqlens and addresses block tables by request: both start at the launch's first request.
+        first = _leading_single_tokens(ctx) if heads // kh <= 64 else 0
+        launches = [(0, first, first, 1)] if first else []
+        tiles = sum(-(-c // 64) for c in lens[first:])
+        if tiles:
+            launches.append((first, len(lens) - first, tiles, 0))
+        if launches and all(0 < tiles <= 65535 for _, _, tiles, _ in launches):
+            for start, requests, tiles, packed in launches:
+                err = _fn("attention_general_tc", "akas_attention_general_tc")(
+                    _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table[start:]), block_table.shape[1],
+                    _ptr(ctx.cu_seqlens[start:]), _ptr(positions), _ptr(out), *options, tiles, heads, kh, d, vd, requests,
+                    packed, _stream())
+                _check(err, "attention_general (tensor cores)")
+            singles = 0
+    if singles:
+        _check(_fn("attention_general", "akas_attention_general")(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions),
+            _ptr(out), *options, singles, heads, kh, d, vd, _code(q), _stream()), "attention_general")
     return out
 
 

@@ -268,8 +268,9 @@ def polynorm(z, coeffs, eps, out_dtype):
 
 
 def decay_gates(low, w_up, bias, tau):
-    """sigmoid(low . w_up^T + bias)^(1 / tau) in float32: [N, O] for low [N, R] (any float dtype), w_up [O, R]."""
-    z = low.to(torch.float64) @ w_up.to(torch.float64).T + bias.to(torch.float64)
+    """sigmoid(low . w_up + bias)^(1 / tau) in float32: [N, O] for low [N, R] (any float dtype), w_up [R, O] (the up
+    matrix of a low-rank pair, transposed)."""
+    z = low.to(torch.float64) @ w_up.to(torch.float64) + bias.to(torch.float64)
     return torch.exp(torch.nn.functional.logsigmoid(z) / tau).to(torch.float32)
 
 

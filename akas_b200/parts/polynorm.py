@@ -2,13 +2,11 @@
 
 act(z) = a N(z) + b N(z^2) + c N(z^3) + e, where the powers are taken element by element, N divides a token's
 row of ``intermediate_size`` values by its root mean square (eps under the root), and a, b, c, e are four
-learned numbers (one tensor [4]). The up product's result stays float32 until the activation has normed it:
-the three root mean squares are float32 sums over the row.
+learned numbers (one tensor [4]). The up product writes the compute dtype, as every product that feeds an
+activation does; the powers, the three root mean squares and the sum of the terms are float32.
 """
 
 from __future__ import annotations
-
-import torch
 
 from .base import FeedForward, Param, project, register_ffn, renamed
 
@@ -36,7 +34,7 @@ class PolyNormMLP(FeedForward):
         self.w_up, self.w_down, self.coeffs = get(self._n("up")), get(self._n("down")), get(self._n("act"))
 
     def forward(self, x, ctx, residual=None):
-        z = project(self.rt, x, self.w_up, out_dtype=torch.float32)
+        z = project(self.rt, x, self.w_up)
         act = self.rt.ops.polynorm(z, self.coeffs, self.spec.eps, self.rt.dtype)
         return project(self.rt, act, self.w_down, residual=residual)
 

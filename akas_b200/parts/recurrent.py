@@ -55,10 +55,11 @@ class GatedLinearAttention(Mixer):
         }
 
     def load(self, get):
-        a1, self.w_up = get(self._n("a1")), get(self._n("a2"))
+        a1, up = get(self._n("a1")), get(self._n("a2"))
         self.rank = a1.shape[0]
-        if self.w_up.shape[1] != self.rank:
-            raise ValueError(f"the decay's two matrices disagree on their rank: {a1.shape[0]} and {self.w_up.shape[1]}")
+        if up.shape[1] != self.rank:
+            raise ValueError(f"the decay's two matrices disagree on their rank: {a1.shape[0]} and {up.shape[1]}")
+        self.w_up = up.t().contiguous()  # [rank, heads * key_dim]: the gates' kernel reads it along its rows
         self.w_in = stack_rows([get(self._n("q")), get(self._n("k")), get(self._n("v")), get(self._n("g")), a1])
         self.b_up = get(self._n("a2.b"))
         self.norm = get(self._n("norm"))

@@ -2,6 +2,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--dtype bfloat16|float32]
     python bench.py --impl reference        (prints why the reference cannot run here)
+    python bench.py --compare gigusun [--shape 1.2b|700m|350m]
+                                            (Gigusun beside LFM2 at equal layer sizes: prefill, decode, time per operation)
 
 A step is one decode step of a batch of 8 requests whose 2,048-token prompts are in the cache
 (context 4,096). ``value`` is decoded tokens a second, timed on the device with CUDA events around
@@ -129,9 +131,20 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batches 1 and 64")
+    ap.add_argument("--compare", choices=("gigusun",), default=None,
+                    help="instead of the default workload: this design beside LFM2 at equal layer sizes, one JSON line each")
+    ap.add_argument("--shape", default="1.2b", help="layer sizes of --compare: 350m, 700m, 1.2b, or several with commas")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
+    if args.compare:
+        from akas_b200.bench import compare_designs
+
+        for shape in args.shape.split(","):
+            for row in compare_designs(shape, steps=min(args.steps, 64), warmup=max(3, min(args.warmup, 8))):
+                row["peaks"] = peaks()
+                print(json.dumps(row), flush=True)
+        return 0
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported")
         return 2

@@ -420,7 +420,7 @@ def test_gates_norms_and_polynorm_kernels(dtype):
     g = torch.Generator().manual_seed(5)
     n = 19
     low = torch.randn(n, 40, generator=g).to(dtype).cuda()[:, 7:18]
-    w_up, bias = torch.randn(50, 11, generator=g).cuda(), torch.randn(50, generator=g).cuda()
+    w_up, bias = torch.randn(11, 50, generator=g).cuda(), torch.randn(50, generator=g).cuda()
     _close(cuda.decay_gates(low, w_up, bias, 8.0), reference.decay_gates(low, w_up, bias, 8.0), 1e-5, "decay gates")
     o = torch.randn(n, 3 * 24, generator=g).cuda()
     gate = torch.randn(n, 100, generator=g).to(dtype).cuda()[:, 9:81]
@@ -430,6 +430,7 @@ def test_gates_norms_and_polynorm_kernels(dtype):
     z = torch.randn(n, 333, generator=g).cuda() * 3
     coeffs = torch.tensor([0.7, -0.4, 0.2, 0.05]).cuda()
     _close(cuda.polynorm(z, coeffs, 1e-6, dtype), reference.polynorm(z, coeffs, 1e-6, dtype), tol, "polynorm")
+    _close(cuda.polynorm(z.to(dtype), coeffs, 1e-6, dtype), reference.polynorm(z.to(dtype), coeffs, 1e-6, dtype), tol, "polynorm")
     h = torch.randn(n, 64, generator=g).cuda()
     table = torch.randn(30, 64, generator=g).to(dtype).cuda()
     idx = torch.randint(0, 30, (n,), generator=g).to(torch.int32).cuda()
@@ -471,8 +472,13 @@ def test_general_attention_kernels(heads, kv_heads, dim, vdim, window, keep, pag
     _close(qn[1], qn[0], tol, "normed q")
     _close(pools[1][0], pools[0][0], tol, "k pages")
     assert torch.equal(pools[1][1], pools[0][1])
+    from types import SimpleNamespace
+
+    # with the step's layout at hand, bfloat16 portions of sizes it takes go to the tensor-core kernel
+    ctx = SimpleNamespace(query_lens=tuple(lengths), decode_only=False, cu_seqlens=cu)
     for sink, cap, bias, gated in ((True, 12.0, True, True), (False, 0.0, False, False), (True, 0.0, False, True)):
         args = (0.3, window, keep, cap, r1 if bias else None, r2 if bias else None, sink, gate if gated else None, page)
         want = reference.attention_general(qn[0], *pools[0], table, seq, pos, *args)
-        got = cuda.attention_general(qn[0], *pools[0], table, seq, pos, *args)
-        _close(got, want, 2e-5 if dtype == torch.float32 else 1.5e-2, f"attention sink={sink} cap={cap} bias={bias}")
+        for layout in (None, ctx):
+            got = cuda.attention_general(qn[0], *pools[0], table, seq, pos, *args, layout)
+            _close(got, want, 2e-5 if dtype == torch.float32 else 1.5e-2, f"attention sink={sink} cap={cap} bias={bias} {layout is None}")
