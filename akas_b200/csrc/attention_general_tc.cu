@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ positions, bf16* __restrict__ out, Options opt, int page_size, int H, int KH,
-                       int D, int V, int R, int packed) {
+                       int D, int V, int R, int packed, int table) {
   constexpr int KSTRIDE = DKP + 8, VSTRIDE = DVP + 8;  // 16 bytes of padding keep ldmatrix conflict-free
   constexpr int KCH = DKP / 8, VCH = DVP / 8;          // 16-byte chunks per row
   constexpr int KS = DKP / 16;                         // k-steps of Q.K^T
@@ -58,6 +58,9 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* k_s = reinterpret_cast<bf16*>(smem_raw);  // [2][BK][KSTRIDE]; stage 0 first holds Q
   bf16* v_s = k_s + 2 * BK * KSTRIDE;             // [2][BK][VSTRIDE]
+  // [table] the head's distance penalty r1 lg2(1 + r2 d) for d = 0 .. window - 1, made once by the block: inside the
+  // window a score then costs a shared-memory read instead of a conversion and a logarithm
+  float* penalty = reinterpret_cast<float*>(v_s + 2 * BK * VSTRIDE);
 
   int tile = (int)gridDim.y - 1 - (int)blockIdx.y, r = 0, n = 0;  // long walks first
   for (; r < R; ++r) {
@@ -138,6 +141,10 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   const float cap2 = opt.cap * kLog2e, scale2 = opt.scale * kLog2e;
 
   load_tile(tile_of(0), 0);
+  if (table > 0) {
+    for (int d = tid; d < table; d += WARPS * 32) penalty[d] = r1[0] * fast_log2(fmaf(r2[0], (float)d, 1.f));
+    __syncthreads();
+  }
   for (int i = 0; i < total; ++i) {
     const int kt = tile_of(i);
     const int stage = i & 1;
@@ -178,7 +185,11 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
         const int qp = qpos[e >> 1];
         const bool seen = key <= qp && (window <= 0 || key > qp - window || key < keep);
         float x = opt.cap > 0.f ? cap2 * fast_tanh(s[nb][e] * opt.scale * inv_cap) : s[nb][e] * scale2;
-        if (biased) x -= r1[e >> 1] * fast_log2(fmaf(r2[e >> 1], (float)(qp - key), 1.f));
+        if (biased) {
+          const int dist = max(qp - key, 0);  // (a key ahead of the query is masked below)
+          if (dist < table) x -= penalty[dist];  // every key inside the window
+          else x -= r1[e >> 1] * fast_log2(fmaf(r2[e >> 1], (float)dist, 1.f));  // kept first tokens far back; no table
+        }
         s[nb][e] = seen ? x : -INFINITY;
         m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
       }
@@ -247,18 +258,23 @@ template <int DKP, int DVP>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* block_table, int max_blocks,
            const int* cu_seqlens, const int* positions, void* out, const Options& opt, int page_size, int tiles, int H,
            int KH, int D, int V, int R, int packed, cudaStream_t stream) {
-  constexpr int smem = 2 * BK * ((DKP + 8) + (DVP + 8)) * (int)sizeof(bf16);
+  // the table of distance penalties: for unpacked launches (one head a block) with a window of at most kTableMost keys
+  constexpr int kTableMost = 8192;
+  const int table = !packed && opt.r1 != nullptr && opt.window > 0 && opt.window <= kTableMost ? opt.window : 0;
+  constexpr int tiles_bytes = 2 * BK * ((DKP + 8) + (DVP + 8)) * (int)sizeof(bf16);
+  const int smem = tiles_bytes + table * (int)sizeof(float);
   static bool configured[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
   if (!configured[device]) {
-    const cudaError_t e = cudaFuncSetAttribute(general_prefill_kernel<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    const cudaError_t e = cudaFuncSetAttribute(general_prefill_kernel<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               tiles_bytes + kTableMost * (int)sizeof(float));
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
   }
   general_prefill_kernel<DKP, DVP><<<dim3(packed ? KH : H, tiles), WARPS * 32, smem, stream>>>(
       (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_seqlens, positions, (bf16*)out,
-      opt, page_size, H, KH, D, V, R, packed);
+      opt, page_size, H, KH, D, V, R, packed, table);
   return launch_status();
 }
 

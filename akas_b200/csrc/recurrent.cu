@@ -161,6 +161,7 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
     }
     __syncthreads();
     if (c0 + CH < t_end) fetch(c0 + CH);
+#pragma unroll 2
     for (int t = 0; t < count; ++t) {
       const float* qr = &sq[t][ks * (R + kPad)];
       const float* kr = &sk[t][ks * (R + kPad)];

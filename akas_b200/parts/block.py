@@ -45,10 +45,11 @@ class Block:
         """Checkpoint name -> Param for everything this block holds."""
         s = self.spec
         out = {s.mixer_prefix + k: v for k, v in self.mixer.params().items()}
+        if self.ffn is not None:
+            out.update({s.ffn_prefix + k: v for k, v in self.ffn.params().items()})
         (norm_param,) = self.mixer_norm.params().values()
         out[s.mixer_norm_name] = norm_param
         if self.ffn is not None:
-            out.update({s.ffn_prefix + k: v for k, v in self.ffn.params().items()})
             (norm_param,) = self.ffn_norm.params().values()
             out[s.ffn_norm_name] = norm_param
         elif s.ffn_norm_name is not None:
