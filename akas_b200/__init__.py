@@ -8,9 +8,9 @@ As in kreasof-ai/akas (src/akas/__init__.py:3-6) the package exports ``Engine``,
 ``Request``.
 """
 
-from .config import EngineConfig, Lfm2Config, load_config, register_architecture
+from .config import EngineConfig, GigusunConfig, Lfm2Config, load_config, register_architecture
 from .engine import Engine, ModelRunner, Request, StepEntry
 
 __version__ = "0.1.0"
-__all__ = ["Engine", "EngineConfig", "Lfm2Config", "ModelRunner", "Request", "StepEntry", "load_config",
+__all__ = ["Engine", "EngineConfig", "GigusunConfig", "Lfm2Config", "ModelRunner", "Request", "StepEntry", "load_config",
            "register_architecture", "__version__"]

@@ -383,8 +383,14 @@ def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), st
     from .ops.timed import TimedOps
     from .weights import write_random_model
 
+    import sys
+
+    def say(what):
+        print(f"[compare] {what}", file=sys.stderr, flush=True)
+
     rows = []
     for design, data in (("lfm2", shape_config(shape)), ("gigusun", gigusun_shape_config(shape))):
+        say(f"{design} {shape}: writing random weights")
         model_config = config_from_dict(data)
         with tempfile.TemporaryDirectory(prefix="akas-bench-") as folder:
             write_random_model(folder, model_config, seed=0, dtype="bfloat16")
@@ -394,17 +400,20 @@ def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), st
             runner = ModelRunner(folder, EngineConfig(**options))
             vocab = runner.vocab_size
             text = synthetic_prompts(1, prompt, vocab)[0]
+            say(f"{design}: prefill of {prompt} tokens")
             pre_ms = measure_prefill(runner, text, repeats=5, warmup=3)
             row = dict(design=design, shape=shape, parameters=sum(matrix_params(runner).values()),
                        prefill=dict(tokens=prompt, ms=round(pre_ms, 3), tokens_per_s=round(prompt / pre_ms * 1e3, 1),
                                     tflops=round(prefill_flops(runner, prompt) / pre_ms / 1e9, 1)), decode={})
             for batch in batches:
+                say(f"{design}: decode at {batch} requests")
                 run = measure_decode(runner, batch, prompt, steps, warmup, repeats=3)
                 row["decode"][str(batch)] = dict(ms_per_step=round(run["ms_per_step"], 4), tokens_per_s=round(run["tokens_per_s"], 1),
                                                  gb_per_s=round(run["bytes"] / run["ms_per_step"] / 1e6, 1),
                                                  kernels=runner.kernels_per_decode_step.get(runner.decode_capacity(batch), 0))
             del runner
             torch.cuda.empty_cache()
+            say(f"{design}: time per operation")
             timed = TimedOps(cuda_ops)
             eager = ModelRunner(folder, EngineConfig(**dict(options, cuda_graphs=False)), ops=timed)
             for _ in range(2):

@@ -235,14 +235,12 @@ AKAS_API int akas_qk_norm_store(const void* q, long long ldq, const void* k, lon
                                 int page_size, int N, int H, int G, int D, int V, int write, int dtype, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (dtype == AKAS_F32)
-    qk_norm_store_kernel<float><<<N, 128, 0, stream>>>((const float*)q, ldq, (const float*)k, ldk, (const float*)v, ldv, qw, kw,
-                                                       eps, (float*)q_out, (float*)k_pool, (float*)v_pool, block_table,
-                                                       max_blocks, seq_of_token, positions, page_size, H, G, D, V, write);
-  else
-    qk_norm_store_kernel<bf16><<<N, 128, 0, stream>>>((const bf16*)q, ldq, (const bf16*)k, ldk, (const bf16*)v, ldv, qw, kw,
-                                                      eps, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks,
-                                                      seq_of_token, positions, page_size, H, G, D, V, write);
-  return launch_status();
+    return launch_ordinary(qk_norm_store_kernel<float>, dim3(N), dim3(128), 0, stream, (const float*)q, ldq, (const float*)k, ldk,
+                          (const float*)v, ldv, qw, kw, eps, (float*)q_out, (float*)k_pool, (float*)v_pool, block_table,
+                          max_blocks, seq_of_token, positions, page_size, H, G, D, V, write);
+  return launch_ordinary(qk_norm_store_kernel<bf16>, dim3(N), dim3(128), 0, stream, (const bf16*)q, ldq, (const bf16*)k, ldk,
+                        (const bf16*)v, ldv, qw, kw, eps, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks,
+                        seq_of_token, positions, page_size, H, G, D, V, write);
 }
 
 template <typename T, typename TG>
@@ -262,10 +260,9 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
     if (e != cudaSuccess) return (int)e;
     allowed[device] = smem;
   }
-  attention_general_kernel<T, TG><<<dim3(N, G), kTile, smem, stream>>>(
-      (const T*)q, (const T*)k_pool, (const T*)v_pool, block_table, max_blocks, seq_of_token, positions, (T*)out, scale, window,
-      keep_first, cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words);
-  return launch_status();
+  return launch_ordinary(attention_general_kernel<T, TG>, dim3(N, G), dim3(kTile), smem, stream, (const T*)q, (const T*)k_pool,
+                        (const T*)v_pool, block_table, max_blocks, seq_of_token, positions, (T*)out, scale, window, keep_first,
+                        cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words);
 }
 
 AKAS_API int akas_attention_general(const void* q, const void* k_pool, const void* v_pool, const int* block_table,

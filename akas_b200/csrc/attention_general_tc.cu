@@ -25,10 +25,12 @@ namespace {
 constexpr int BQ = 64, BK = 64, WARPS = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// tanh(x) = 1 - 2 / (e^(2x) + 1) from the special-function unit's exp2 and reciprocal: an absolute error of a few
+// 1e-7. (tanh.approx.f32 is good to about 5e-4 only, which the cap in front of it, often 20 to 50, would turn into
+// errors of the scores as large as the rounding of bfloat16.)
 __device__ __forceinline__ float fast_tanh(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
+  const float e = fast_exp2(fminf(x * (2.f * kLog2e), 80.f));
+  return 1.f - __fdividef(2.f, e + 1.f);
 }
 __device__ __forceinline__ float fast_log2(float x) {
   float y;
@@ -45,8 +47,10 @@ struct Options {
   long long ldg;
 };
 
+constexpr int kTableBefore = 128, kTableAfter = 192;  // entries of the penalty table on either side of the window's distances
+
 template <int DKP, int DVP>  // head sizes rounded up to multiples of 32
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, (DKP + DVP <= 192) ? 3 : 2)
 general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ positions, bf16* __restrict__ out, Options opt, int page_size, int H, int KH,
@@ -58,9 +62,11 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* k_s = reinterpret_cast<bf16*>(smem_raw);  // [2][BK][KSTRIDE]; stage 0 first holds Q
   bf16* v_s = k_s + 2 * BK * KSTRIDE;             // [2][BK][VSTRIDE]
-  // [table] the head's distance penalty r1 lg2(1 + r2 d) for d = 0 .. window - 1, made once by the block: inside the
-  // window a score then costs a shared-memory read instead of a conversion and a logarithm
-  float* penalty = reinterpret_cast<float*>(v_s + 2 * BK * VSTRIDE);
+  // [table + kTableBefore + kTableAfter] the head's distance penalty r1 lg2(1 + r2 d), made once by the block, for
+  // every distance that a tile without kept first tokens can hold: d from -126 (a key ahead of the query, masked) to
+  // window + 125 (a key of the window's first tile that lies before the window, masked). A score then costs a
+  // shared-memory read instead of a conversion and a logarithm, and the read needs no bounds.
+  float* penalty = reinterpret_cast<float*>(v_s + 2 * BK * VSTRIDE) + kTableBefore;
 
   int tile = (int)gridDim.y - 1 - (int)blockIdx.y, r = 0, n = 0;  // long walks first
   for (; r < R; ++r) {
@@ -142,9 +148,12 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
 
   load_tile(tile_of(0), 0);
   if (table > 0) {
-    for (int d = tid; d < table; d += WARPS * 32) penalty[d] = r1[0] * fast_log2(fmaf(r2[0], (float)d, 1.f));
+    for (int d = tid - kTableBefore; d < table + kTableAfter; d += WARPS * 32)
+      penalty[d] = d > 0 ? r1[0] * fast_log2(fmaf(r2[0], (float)d, 1.f)) : 0.f;
     __syncthreads();
   }
+  const int wlimit = window > 0 ? window : 0x7fffffff;
+  const float scale_cap = opt.scale * inv_cap;
   for (int i = 0; i < total; ++i) {
     const int kt = tile_of(i);
     const int stage = i & 1;
@@ -177,21 +186,35 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     }
 
     float m_new[2] = {m_run[0], m_run[1]};
+    // A tile without kept first tokens (all but a request's first few): a key is seen iff 0 <= distance < window, and
+    // the penalty of every distance in it is in the table (where there is a penalty, there must be a table).
+    const bool fast = kt * BK >= keep && (!biased || table > 0);
+    if (fast) {
+      const int dbase[2] = {qpos[0] - (kt * BK + 2 * t), qpos[1] - (kt * BK + 2 * t)};
 #pragma unroll
-    for (int nb = 0; nb < BK / 8; ++nb) {
+      for (int nb = 0; nb < BK / 8; ++nb) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = kt * BK + nb * 8 + 2 * t + (e & 1);
-        const int qp = qpos[e >> 1];
-        const bool seen = key <= qp && (window <= 0 || key > qp - window || key < keep);
-        float x = opt.cap > 0.f ? cap2 * fast_tanh(s[nb][e] * opt.scale * inv_cap) : s[nb][e] * scale2;
-        if (biased) {
-          const int dist = max(qp - key, 0);  // (a key ahead of the query is masked below)
-          if (dist < table) x -= penalty[dist];  // every key inside the window
-          else x -= r1[e >> 1] * fast_log2(fmaf(r2[e >> 1], (float)dist, 1.f));  // kept first tokens far back; no table
+        for (int e = 0; e < 4; ++e) {
+          const int dist = dbase[e >> 1] - (nb * 8 + (e & 1));
+          float x = opt.cap > 0.f ? cap2 * fast_tanh(s[nb][e] * scale_cap) : s[nb][e] * scale2;
+          if (biased) x -= penalty[dist];
+          s[nb][e] = (unsigned)dist < (unsigned)wlimit ? x : -INFINITY;
+          m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
         }
-        s[nb][e] = seen ? x : -INFINITY;
-        m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
+      }
+    } else {
+#pragma unroll
+      for (int nb = 0; nb < BK / 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = kt * BK + nb * 8 + 2 * t + (e & 1);
+          const int qp = qpos[e >> 1];
+          const bool seen = key <= qp && (window <= 0 || key > qp - window || key < keep);
+          float x = opt.cap > 0.f ? cap2 * fast_tanh(s[nb][e] * scale_cap) : s[nb][e] * scale2;
+          if (biased) x -= r1[e >> 1] * fast_log2(fmaf(r2[e >> 1], (float)max(qp - key, 0), 1.f));
+          s[nb][e] = seen ? x : -INFINITY;
+          m_new[e >> 1] = fmaxf(m_new[e >> 1], s[nb][e]);
+        }
       }
     }
     float corr[2], m_use[2];
@@ -262,20 +285,19 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
   constexpr int kTableMost = 8192;
   const int table = !packed && opt.r1 != nullptr && opt.window > 0 && opt.window <= kTableMost ? opt.window : 0;
   constexpr int tiles_bytes = 2 * BK * ((DKP + 8) + (DVP + 8)) * (int)sizeof(bf16);
-  const int smem = tiles_bytes + table * (int)sizeof(float);
+  const int smem = tiles_bytes + (table ? table + kTableBefore + kTableAfter : 0) * (int)sizeof(float);
   static bool configured[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
   if (!configured[device]) {
     const cudaError_t e = cudaFuncSetAttribute(general_prefill_kernel<DKP, DVP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               tiles_bytes + kTableMost * (int)sizeof(float));
+                                               tiles_bytes + (kTableMost + kTableBefore + kTableAfter) * (int)sizeof(float));
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
   }
-  general_prefill_kernel<DKP, DVP><<<dim3(packed ? KH : H, tiles), WARPS * 32, smem, stream>>>(
-      (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_seqlens, positions, (bf16*)out,
-      opt, page_size, H, KH, D, V, R, packed, table);
-  return launch_status();
+  return launch_ordinary(general_prefill_kernel<DKP, DVP>, dim3(packed ? KH : H, tiles), dim3(WARPS * 32), (size_t)smem, stream,
+                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_seqlens, positions,
+                        (bf16*)out, opt, page_size, H, KH, D, V, R, packed, table);
 }
 
 }  // namespace

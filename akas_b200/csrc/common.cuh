@@ -128,6 +128,21 @@ static inline int launch_chained(void (*kernel)(Params...), dim3 grid, dim3 bloc
   return (int)cudaLaunchKernelEx(&config, kernel, Params(args)...);
 }
 
+// The same call without the attribute: the kernel starts when everything before it on the stream has completed. For
+// kernels that do not call chain_wait(). (The kernels of the matrix-state mixers and of the general attention are
+// launched this way: as programmatic dependents, steps that hold several long prompt portions stalled on a B200, and
+// ran to their end with AKAS_B200_CHAINED_LAUNCHES=0; reading did not show why.)
+template <typename... Params, typename... Args>
+static inline int launch_ordinary(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  return (int)cudaLaunchKernelEx(&config, kernel, Params(args)...);
+}
+
 inline bool chained_launches_enabled() {
   static const bool enabled = [] {
     const char* v = getenv("AKAS_B200_CHAINED_LAUNCHES");

@@ -254,9 +254,8 @@ __global__ void add_rows_kernel(float* __restrict__ h, const T* __restrict__ tab
 AKAS_API int akas_add_rows(float* h, const void* table, const int* index, int N, int C, int dtype, cudaStream_t stream) {
   if (N <= 0) return 0;
   const int threads = C >= 1024 ? 256 : 128;
-  if (dtype == AKAS_F32) add_rows_kernel<float><<<N, threads, 0, stream>>>(h, (const float*)table, index, C);
-  else add_rows_kernel<bf16><<<N, threads, 0, stream>>>(h, (const bf16*)table, index, C);
-  return launch_status();
+  if (dtype == AKAS_F32) return launch_ordinary(add_rows_kernel<float>, dim3(N), dim3(threads), 0, stream, h, (const float*)table, index, C);
+  return launch_ordinary(add_rows_kernel<bf16>, dim3(N), dim3(threads), 0, stream, h, (const bf16*)table, index, C);
 }
 
 // PolyNorm of rows: out = a N(z) + b N(z^2) + c N(z^3) + e with N(x) = x / sqrt(mean(x^2) + eps) over the row and
@@ -327,13 +326,12 @@ AKAS_API int akas_polynorm(const void* z, const float* coeffs, float eps, void* 
   const bool vec = F % 8 == 0 && (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0;
 #define AKAS_POLY(TI, TO)                                                                                              \
   {                                                                                                                    \
-    if (vec) polynorm_kernel<TI, TO, true><<<N, threads, 0, stream>>>((const TI*)z, coeffs, eps, (TO*)out, F);         \
-    else polynorm_kernel<TI, TO, false><<<N, threads, 0, stream>>>((const TI*)z, coeffs, eps, (TO*)out, F);            \
+    if (vec) return launch_ordinary(polynorm_kernel<TI, TO, true>, dim3(N), dim3(threads), 0, stream, (const TI*)z, coeffs, eps, (TO*)out, F);  \
+    return launch_ordinary(polynorm_kernel<TI, TO, false>, dim3(N), dim3(threads), 0, stream, (const TI*)z, coeffs, eps, (TO*)out, F);          \
   }
   if (in_dtype == AKAS_F32 && out_dtype == AKAS_F32) AKAS_POLY(float, float)
   else if (in_dtype == AKAS_F32) AKAS_POLY(float, bf16)
   else if (out_dtype == AKAS_F32) AKAS_POLY(bf16, float)
   else AKAS_POLY(bf16, bf16)
 #undef AKAS_POLY
-  return launch_status();
 }

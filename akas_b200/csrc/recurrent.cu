@@ -229,10 +229,8 @@ int launch_scan(const T* q, long long ldq, const T* k, long long ldk, const T* v
 #define AKAS_SCAN(R, KS, CH)                                                                                              \
   {                                                                                                                       \
     const dim3 grid(H, requests, (V + 256 / KS - 1) / (256 / KS));                                                        \
-    scan_kernel<T, R, KS, CH, 256, DELTA><<<grid, 256, 0, stream>>>(q, ldq, k, ldk, v, ldv, decay, beta, state,           \
-                                                                    slot_stride, cu_seqlens, slots, out, H, rep, D, V,    \
-                                                                    q_scale, write);                                      \
-    return launch_status();                                                                                               \
+    return launch_ordinary(scan_kernel<T, R, KS, CH, 256, DELTA>, grid, dim3(256), 0, stream, q, ldq, k, ldk, v, ldv, decay,  \
+                          beta, state, slot_stride, cu_seqlens, slots, out, H, rep, D, V, q_scale, write);                \
   }
   if (D <= 8) AKAS_SCAN(8, 1, 16)
   if (D <= 16) AKAS_SCAN(8, 2, 16)
@@ -270,6 +268,46 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, long long ldx, 
       acc = fmaf(taps[(size_t)c * L + j], in, acc);
     }
     y[(size_t)n * C + c] = acc * sigmoid_f(acc);
+  }
+}
+
+// The same for four neighbouring channels a thread (C, the row pitches and the slot pitch multiples of 4, rows on 16
+// bytes): inputs move 8 or 16 bytes at a time, results 16.
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+  const uint2 a = *reinterpret_cast<const uint2*>(p);
+  v[0] = __uint_as_float(a.x << 16); v[1] = __uint_as_float(a.x & 0xffff0000u);
+  v[2] = __uint_as_float(a.y << 16); v[3] = __uint_as_float(a.y & 0xffff0000u);
+}
+
+template <typename T>
+__global__ void causal_conv_silu4_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ taps,
+                                         const float* __restrict__ state, long long slot_stride,
+                                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token,
+                                         const int* __restrict__ slots, float* __restrict__ y, int C, int L) {
+  const int n = blockIdx.x;
+  const int req = seq_of_token[n];
+  if (req < 0) return;
+  const int slot = slots[req];
+  if (slot < 0) return;
+  const int first = cu_seqlens[req];
+  const int i = n - first;
+  const float* st = state + (size_t)slot * slot_stride;
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < C; c += gridDim.y * blockDim.x * 4) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < L; ++j) {
+      const int src = i - (L - 1) + j;
+      float in[4];
+      if (src >= 0) load4(x + (size_t)(first + src) * ldx + c, in);
+      else load4(st + (size_t)(L - 1 + src) * C + c, in);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] = fmaf(taps[(size_t)(c + e) * L + j], in[e], acc[e]);
+    }
+    *reinterpret_cast<float4*>(y + (size_t)n * C + c) =
+        make_float4(acc[0] * sigmoid_f(acc[0]), acc[1] * sigmoid_f(acc[1]), acc[2] * sigmoid_f(acc[2]), acc[3] * sigmoid_f(acc[3]));
   }
 }
 
@@ -330,6 +368,31 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
   const int n = (int)(item / H), h = (int)(item % H);
   const float* row = o + (size_t)n * H * V + (size_t)h * V;
   float ss = 0.f;
+  if (V % 4 == 0 && ldg % 4 == 0 && sizeof(TO) == sizeof(TG) && (uintptr_t)gate % (4 * sizeof(TG)) == 0) {
+    // four channels a lane: 16-byte reads of o, 8- or 16-byte reads of the gate and writes of the result
+    for (int j = lane * 4; j < V; j += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(row + j);
+      ss = fmaf(x.x, x.x, ss); ss = fmaf(x.y, x.y, ss); ss = fmaf(x.z, x.z, ss); ss = fmaf(x.w, x.w, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)V + eps);
+    for (int j = lane * 4; j < V; j += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(row + j);
+      const float4 wv = *reinterpret_cast<const float4*>(w + j);
+      float gv[4];
+      load4(gate + (size_t)n * ldg + (size_t)h * V + j, gv);
+      const float r[4] = {x.x * inv * wv.x * (gv[0] * sigmoid_f(gv[0])), x.y * inv * wv.y * (gv[1] * sigmoid_f(gv[1])),
+                          x.z * inv * wv.z * (gv[2] * sigmoid_f(gv[2])), x.w * inv * wv.w * (gv[3] * sigmoid_f(gv[3]))};
+      TO* dst = out + (size_t)n * H * V + (size_t)h * V + j;
+      if (sizeof(TO) == 4) {
+        *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+      } else {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(r[0], r[1]), b = __floats2bfloat162_rn(r[2], r[3]);
+        *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+      }
+    }
+    return;
+  }
   for (int j = lane; j < V; j += 32) ss = fmaf(row[j], row[j], ss);
   ss = warp_sum(ss);
   const float inv = 1.f / sqrtf(ss / (float)V + eps);
@@ -348,10 +411,8 @@ AKAS_API int akas_decay_gates(const void* low, long long ld, const float* w, con
   const size_t smem = (size_t)kGateTokens * R * sizeof(float);
   if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
   if (dtype == AKAS_F32)
-    decay_gates_kernel<float><<<grid, 128, smem, stream>>>((const float*)low, ld, w, bias, out, N, O, R, 1.f / tau);
-  else
-    decay_gates_kernel<bf16><<<grid, 128, smem, stream>>>((const bf16*)low, ld, w, bias, out, N, O, R, 1.f / tau);
-  return launch_status();
+    return launch_ordinary(decay_gates_kernel<float>, grid, dim3(128), smem, stream, (const float*)low, ld, w, bias, out, N, O, R, 1.f / tau);
+  return launch_ordinary(decay_gates_kernel<bf16>, grid, dim3(128), smem, stream, (const bf16*)low, ld, w, bias, out, N, O, R, 1.f / tau);
 }
 
 AKAS_API int akas_gla_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
@@ -379,20 +440,28 @@ AKAS_API int akas_causal_conv_silu(const void* x, long long ldx, const float* ta
                                    int requests, int C, int L, int write, int dtype, cudaStream_t stream) {
   if (N <= 0 || C <= 0) return 0;
   const dim3 grid(N, min((C + 255) / 256, 32));
-  if (dtype == AKAS_F32)
-    causal_conv_silu_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, ldx, taps, state, slot_stride, cu_seqlens,
-                                                            seq_of_token, slots, y, C, L);
-  else
-    causal_conv_silu_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)x, ldx, taps, state, slot_stride, cu_seqlens,
-                                                           seq_of_token, slots, y, C, L);
-  int err = launch_status();
+  const float* old = state;
+  const size_t elem = dtype == AKAS_F32 ? 4 : 2;
+  const bool four = C % 4 == 0 && ldx % 4 == 0 && slot_stride % 4 == 0 && (uintptr_t)x % (4 * elem) == 0 &&
+                    (uintptr_t)state % 16 == 0 && (uintptr_t)y % 16 == 0;
+  const dim3 grid4(N, min((C / 4 + 127) / 128, 32));
+  int err = four ? (dtype == AKAS_F32
+      ? launch_ordinary(causal_conv_silu4_kernel<float>, grid4, dim3(128), 0, stream, (const float*)x, ldx, taps, old, slot_stride,
+                        cu_seqlens, seq_of_token, slots, y, C, L)
+      : launch_ordinary(causal_conv_silu4_kernel<bf16>, grid4, dim3(128), 0, stream, (const bf16*)x, ldx, taps, old, slot_stride,
+                        cu_seqlens, seq_of_token, slots, y, C, L))
+      : dtype == AKAS_F32
+      ? launch_ordinary(causal_conv_silu_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, ldx, taps, old, slot_stride,
+                       cu_seqlens, seq_of_token, slots, y, C, L)
+      : launch_ordinary(causal_conv_silu_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)x, ldx, taps, old, slot_stride,
+                       cu_seqlens, seq_of_token, slots, y, C, L);
   if (err || !write || requests <= 0) return err;
   const dim3 sgrid(requests, min((C + 255) / 256, 32));
   if (dtype == AKAS_F32)
-    causal_conv_state_kernel<float><<<sgrid, 256, 0, stream>>>((const float*)x, ldx, state, slot_stride, cu_seqlens, slots, C, L);
-  else
-    causal_conv_state_kernel<bf16><<<sgrid, 256, 0, stream>>>((const bf16*)x, ldx, state, slot_stride, cu_seqlens, slots, C, L);
-  return launch_status();
+    return launch_ordinary(causal_conv_state_kernel<float>, sgrid, dim3(256), 0, stream, (const float*)x, ldx, state, slot_stride,
+                          cu_seqlens, slots, C, L);
+  return launch_ordinary(causal_conv_state_kernel<bf16>, sgrid, dim3(256), 0, stream, (const bf16*)x, ldx, state, slot_stride,
+                        cu_seqlens, slots, C, L);
 }
 
 AKAS_API int akas_delta_prep(float* y, long long ldy, int G, int D, float q_scale, float unit_eps, const void* b,
@@ -400,12 +469,10 @@ AKAS_API int akas_delta_prep(float* y, long long ldy, int G, int D, float q_scal
                              float* beta, float* g, int N, int H, int dtype, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (dtype == AKAS_F32)
-    delta_prep_kernel<float><<<N, 128, 0, stream>>>(y, ldy, G, D, q_scale, unit_eps, (const float*)b, ldb, (const float*)a,
-                                                    lda, a_log, dt_bias, beta, g, H);
-  else
-    delta_prep_kernel<bf16><<<N, 128, 0, stream>>>(y, ldy, G, D, q_scale, unit_eps, (const bf16*)b, ldb, (const bf16*)a, lda,
-                                                   a_log, dt_bias, beta, g, H);
-  return launch_status();
+    return launch_ordinary(delta_prep_kernel<float>, dim3(N), dim3(128), 0, stream, y, ldy, G, D, q_scale, unit_eps,
+                          (const float*)b, ldb, (const float*)a, lda, a_log, dt_bias, beta, g, H);
+  return launch_ordinary(delta_prep_kernel<bf16>, dim3(N), dim3(128), 0, stream, y, ldy, G, D, q_scale, unit_eps, (const bf16*)b,
+                        ldb, (const bf16*)a, lda, a_log, dt_bias, beta, g, H);
 }
 
 AKAS_API int akas_gated_rmsnorm(const float* o, const float* w, float eps, const void* gate, long long ldg, void* out, int N,
@@ -414,11 +481,10 @@ AKAS_API int akas_gated_rmsnorm(const float* o, const float* w, float eps, const
   const long long items = (long long)N * H;
   const int blocks = (int)((items + 7) / 8);
 #define AKAS_GN(TG, TO) \
-  gated_rmsnorm_kernel<TG, TO><<<blocks, 256, 0, stream>>>(o, w, eps, (const TG*)gate, ldg, (TO*)out, N, H, V)
+  return launch_ordinary(gated_rmsnorm_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, o, w, eps, (const TG*)gate, ldg, (TO*)out, N, H, V)
   if (gate_dtype == AKAS_F32 && out_dtype == AKAS_F32) AKAS_GN(float, float);
-  else if (gate_dtype == AKAS_F32) AKAS_GN(float, bf16);
-  else if (out_dtype == AKAS_F32) AKAS_GN(bf16, float);
-  else AKAS_GN(bf16, bf16);
+  if (gate_dtype == AKAS_F32) AKAS_GN(float, bf16);
+  if (out_dtype == AKAS_F32) AKAS_GN(bf16, float);
+  AKAS_GN(bf16, bf16);
 #undef AKAS_GN
-  return launch_status();
 }

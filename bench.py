@@ -140,6 +140,12 @@ def main():
     if args.compare:
         from akas_b200.bench import compare_designs
 
+        watchdog = float(os.environ.get("AKAS_B200_BENCH_WATCHDOG", "0"))
+        if watchdog > 0:  # where every thread stands, to stderr, every so many seconds: a run that stalls says where
+            import faulthandler
+
+            faulthandler.dump_traceback_later(watchdog, repeat=True)
+
         for shape in args.shape.split(","):
             for row in compare_designs(shape, steps=min(args.steps, 64), warmup=max(3, min(args.warmup, 8))):
                 row["peaks"] = peaks()
