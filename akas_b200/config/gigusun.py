@@ -116,7 +116,7 @@ class GigusunConfig:
                 if "rank" in m:
                     _int(where, m, "rank")
             else:
-                _int(where, m, "conv", least=2)
+                _int(where, m, "conv")
             mlp = entry.get("mlp")
             ff = None
             if mlp is not None:

@@ -313,7 +313,7 @@ def causal_conv_silu(x, taps, state, cu_seqlens, seq_of_token, slots, write=True
         for j in range(l):
             acc = acc + hist[j : j + b - a] * taps[:, j]
         out[a:b] = acc * torch.sigmoid(acc)
-        if write:
+        if write and l > 1:
             state[slot] = hist[-(l - 1):]
     return out
 

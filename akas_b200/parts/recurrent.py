@@ -96,8 +96,8 @@ class GatedDelta(Mixer):
         s = spec
         if s.num_heads % s.num_kv_heads:
             raise ValueError(f"{s.num_heads} heads are not a multiple of {s.num_kv_heads} query/key heads")
-        if not 2 <= s.conv_kernel <= 16:
-            raise ValueError(f"conv_kernel {s.conv_kernel} must be from 2 to 16")
+        if not 1 <= s.conv_kernel <= 64:
+            raise ValueError(f"conv_kernel {s.conv_kernel} must be from 1 to 64")
         self.channels = 2 * s.num_kv_heads * s.key_dim + s.num_heads * s.value_dim  # what the convolution runs over
         self.w_in = self.w_out = self.taps = self.a_log = self.dt_bias = self.norm = None
 

@@ -23,6 +23,7 @@ GLA = dict(heads=3, dim=20, vdim=24, tau=8.0, rank=6)
 GLA_BIG = dict(heads=2, dim=72, vdim=136, tau=4.0, rank=5)
 DELTA = dict(heads=4, kv_heads=4, dim=16, vdim=12, conv=4)
 DELTA_SHARED = dict(heads=6, kv_heads=2, dim=40, vdim=20, conv=2)
+DELTA_ONE_TAP = dict(heads=2, kv_heads=1, dim=24, vdim=28, conv=1)
 
 
 def layer(kind, mixer, ff=112):
@@ -38,7 +39,7 @@ CONFIGS = {
     "gla": dict(architecture="Gigusun", width=56, vocab=90, max_positions=512, norm=dict(eps=1e-6),
                 layers=[layer("gla", GLA, ff=None), layer("gla", GLA_BIG, ff=72)]),
     "delta": dict(architecture="Gigusun", width=64, vocab=100, max_positions=512, norm=dict(eps=1e-4),
-                  layers=[layer("delta", DELTA_SHARED, ff=None), layer("delta", DELTA, ff=40)]),
+                  layers=[layer("delta", DELTA_SHARED, ff=None), layer("delta", DELTA, ff=40), layer("delta", DELTA_ONE_TAP, ff=None)]),
 }
 PAGE = {"mix": 8, "attention": 16, "gla": 64, "delta": 8}
 LENGTHS = {"mix": [1, 45, 2, 97, 33, 130, 64], "attention": [70, 3, 41, 100], "gla": [90, 1, 37], "delta": [5, 80, 2, 33]}
