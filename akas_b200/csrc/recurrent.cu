@@ -111,7 +111,9 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
   // A chunk's inputs are fetched into registers while the chunk before it is computed, and put into shared memory
   // when that is done: the recurrence never waits for global memory except at its first chunk.
   constexpr int NQ = (CH * KS * R + TH - 1) / TH, NV = (CH * VT + TH - 1) / TH;
-  float rq[NQ], rk[NQ], ra[DELTA ? 1 : NQ], rv[NV], rg = 0.f, rb = 0.f;
+  T rq[NQ], rk[NQ], rv[NV];  // as fetched: widening them here would make the loop below wait for the loads at once
+  float ra[DELTA ? 1 : NQ], rg = 0.f, rb = 0.f;
+  const T zero = from_f32<T>(0.f);
   auto fetch = [&](int c0) {
     const int count = min(CH, t_end - c0);
 #pragma unroll
@@ -120,15 +122,15 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
       const int t = i / (KS * R), kk = i % (KS * R);
       const bool in = t < count && kk < D;
       const size_t n = (size_t)(c0 + t);
-      rq[u] = in ? to_f32(q[n * ldq + (size_t)hk * D + kk]) * q_scale : 0.f;
-      rk[u] = in ? to_f32(k[n * ldk + (size_t)hk * D + kk]) : 0.f;
+      rq[u] = in ? q[n * ldq + (size_t)hk * D + kk] : zero;
+      rk[u] = in ? k[n * ldk + (size_t)hk * D + kk] : zero;
       if (!DELTA) ra[u] = in ? decay[n * ((size_t)H * D) + (size_t)h * D + kk] : 0.f;
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
       const int i = threadIdx.x + u * TH;
       const int t = i / VT, col = blockIdx.z * VT + i % VT;
-      rv[u] = t < count && col < V ? to_f32(v[(size_t)(c0 + t) * ldv + (size_t)h * V + col]) : 0.f;
+      rv[u] = t < count && col < V ? v[(size_t)(c0 + t) * ldv + (size_t)h * V + col] : zero;
     }
     if (DELTA && threadIdx.x < count) {
       rg = decay[(size_t)(c0 + threadIdx.x) * H + h];
@@ -145,15 +147,15 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
       if (i < CH * KS * R) {
         const int t = i / (KS * R), kk = i % (KS * R);
         const int at = kk + (kk / R) * kPad;
-        sq[t][at] = rq[u];
-        sk[t][at] = rk[u];
+        sq[t][at] = to_f32(rq[u]) * q_scale;
+        sk[t][at] = to_f32(rk[u]);
         if (!DELTA) sa[t][at] = ra[u];
       }
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
       const int i = threadIdx.x + u * TH;
-      if (i < CH * VT) sv[i / VT][i % VT] = rv[u];
+      if (i < CH * VT) sv[i / VT][i % VT] = to_f32(rv[u]);
     }
     if (DELTA && threadIdx.x < CH) {
       sg[threadIdx.x] = rg;
