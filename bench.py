@@ -3,7 +3,9 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--dtype bfloat16|float32]
     python bench.py --impl reference        (prints why the reference cannot run here)
     python bench.py --compare gigusun [--shape 1.2b|700m|350m]
-                                            (Gigusun beside LFM2 at equal layer sizes: prefill, decode, time per operation)
+                                            (Gigusun beside LFM2 at equal layer sizes: prefill, decode, time per operation;
+                                             AKAS_B200_BENCH_WATCHDOG=seconds prints every thread's stack to stderr at
+                                             that interval, so that a run that stalls says where)
 
 A step is one decode step of a batch of 8 requests whose 2,048-token prompts are in the cache
 (context 4,096). ``value`` is decoded tokens a second, timed on the device with CUDA events around
