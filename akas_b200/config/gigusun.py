@@ -195,7 +195,7 @@ class GigusunConfig:
             embedding_name="embed",
             final_norm_name="final.norm",
             head_name="head",
-            head_optional=True,  # a folder without the tensor uses the embedding as its head
+            head_optional=False,
             max_context=self.max_positions,
             position_table_name="pos",
             embedding_norm=norm,
