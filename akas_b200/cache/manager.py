@@ -105,7 +105,8 @@ class _Request:
 class CacheManager:
     def __init__(self, cache_specs: Sequence, page_size: int, pool_tokens: int, max_requests: int,
                  context: int, dtype=torch.float32, device="cpu", storage: bool = True):
-        """``cache_specs``: for each schedule entry the spec its mixer asked for, or None.
+        """``cache_specs``: for each schedule entry the spec its mixer asked for, or None; a tuple of specs for a
+        mixer that holds several mixers.
 
         Every group gets ``pool_tokens // its page size`` pages (the engine's ``page_size`` unless the group's
         specs name their own); a request may hold up to ``context`` tokens, so a group's block table has
@@ -128,9 +129,17 @@ class CacheManager:
         # states of one shape and type share an allocation, so that a slot is zeroed across layers by one launch
         backing: Dict[tuple, torch.Tensor] = {}
         taken: Dict[tuple, int] = {}
+
+        def flat(specs):
+            for spec in specs:
+                if isinstance(spec, (tuple, list)):
+                    yield from flat(spec)
+                else:
+                    yield spec
+
         if storage:
             count: Dict[tuple, int] = {}
-            for spec in cache_specs:
+            for spec in flat(cache_specs):
                 if isinstance(spec, StateSpec):
                     key = (tuple(spec.shape), spec.dtype)
                     count[key] = count.get(key, 0) + 1
@@ -138,10 +147,15 @@ class CacheManager:
                 backing[key] = torch.zeros((layers, max_requests, *key[0]), dtype=key[1], device=device)
                 taken[key] = 0
                 self.state_tensors.append(backing[key])
-        for spec in cache_specs:
+
+        def view(spec):
+            """What the mixer that asked with ``spec`` gets; a mixer made of several mixers asks with a tuple of specs and
+            gets a tuple of views, each as if its branch had asked alone."""
+            if isinstance(spec, (tuple, list)):
+                return tuple(view(inner) for inner in spec)
             if spec is None:
-                self.views.append(None)
-            elif isinstance(spec, PagedSpec):
+                return None
+            if isinstance(spec, PagedSpec):
                 size = spec.page_size or page_size
                 if size < 1 or pool_tokens < size:
                     raise ValueError(f"pool of {pool_tokens} tokens holds no page of {size}")
@@ -157,16 +171,17 @@ class CacheManager:
                     pages = self.groups[gid].allocator.num_pages
                     pools = {name: torch.zeros((pages, *shape), dtype=spec.dtype or dtype, device=device)
                              for name, shape in spec.pools(size).items()}
-                self.views.append(PagedCache(pools, gid, size, spec))
-            elif isinstance(spec, StateSpec):
+                return PagedCache(pools, gid, size, spec)
+            if isinstance(spec, StateSpec):
                 state = None
                 if storage:
                     key = (tuple(spec.shape), spec.dtype)
                     state = backing[key][taken[key]]
                     taken[key] += 1
-                self.views.append(StateCache(state, spec))
-            else:
-                raise TypeError(f"unknown cache spec {spec!r}")
+                return StateCache(state, spec)
+            raise TypeError(f"unknown cache spec {spec!r}")
+
+        self.views = [view(spec) for spec in cache_specs]
 
     # ------------------------------------------------------------------ requests
 

@@ -3,6 +3,8 @@
 from .engine import EngineConfig
 from .gigusun import ARCHITECTURE as GIGUSUN_ARCHITECTURE
 from .gigusun import GigusunConfig
+from .girelix import ARCHITECTURE as GIRELIX_ARCHITECTURE
+from .girelix import GirelixConfig
 from .lfm2 import ARCHITECTURE as LFM2_ARCHITECTURE
 from .lfm2 import ConfigError, Lfm2Config
 from .registry import (
@@ -14,14 +16,17 @@ from .registry import (
 )
 from .specs import (
     AttentionSpec,
+    DecayedLinearAttentionSpec,
     GatedDeltaSpec,
     GatedLinearAttentionSpec,
     LayerSpec,
     ModelSpec,
+    ParallelMixerSpec,
     PartSpec,
     PolyNormMLPSpec,
     RMSNormSpec,
     RopeSpec,
+    RoutedExpertsSpec,
     ScheduleEntry,
     ShortConvSpec,
     SwiGLUSpec,
@@ -29,9 +34,10 @@ from .specs import (
 
 register_architecture(LFM2_ARCHITECTURE, Lfm2Config, model_type="lfm2")
 register_architecture(GIGUSUN_ARCHITECTURE, GigusunConfig)
+register_architecture(GIRELIX_ARCHITECTURE, GirelixConfig)
 
 __all__ = [
-    "AttentionSpec", "ConfigError", "EngineConfig", "GatedDeltaSpec", "GatedLinearAttentionSpec", "GigusunConfig", "LayerSpec",
+    "AttentionSpec", "ConfigError", "DecayedLinearAttentionSpec", "GirelixConfig", "ParallelMixerSpec", "RoutedExpertsSpec", "EngineConfig", "GatedDeltaSpec", "GatedLinearAttentionSpec", "GigusunConfig", "LayerSpec",
     "Lfm2Config", "ModelSpec", "PartSpec", "PolyNormMLPSpec",
     "RMSNormSpec", "RopeSpec", "ScheduleEntry", "ShortConvSpec", "SwiGLUSpec", "architecture_of",
     "architectures", "config_from_dict", "load_config", "register_architecture",

@@ -38,12 +38,15 @@ class RMSNormSpec:
 
 @dataclass(frozen=True)
 class RopeSpec:
-    """Rotate-half rotary encoding of the first ``rotary_dim`` channels of each head."""
+    """Rotary encoding of the first ``rotary_dim`` channels of each head: channel i turns with channel
+    i + rotary / 2 (rotate-half), or, ``interleaved``, channel 2i with channel 2i + 1; the angle of pair i at
+    position p is p * theta^(-2i / rotary) either way."""
 
     head_dim: int
     theta: float
     rotary_dim: Optional[int] = None  # None: the whole head
     kind: str = "rope"
+    interleaved: bool = False  # only the general attention kernels take it
 
     @property
     def rotary(self) -> int:
@@ -69,8 +72,13 @@ class AttentionSpec:
     softcap: Optional[float] = None  # score <- cap * tanh(score / cap), after the scale
     distance_bias: bool = False  # score <- score - r1_h * ln(1 + r2_h * (i - j)); r1, r2 are two tensors [heads]
     keep_first: int = 0  # with a window: the first keep_first positions of a request stay visible behind it
-    sink: bool = False  # one more term exp(0) in the softmax's denominator; it has no value
+    # one more term in the softmax's denominator, without a key or a value: True: exp(0); "learned": exp(sink_h) with
+    # a tensor [heads] of logits, which the scale does not touch
+    sink: Any = False
     gate: Optional[str] = None  # "head": head h's output times sigmoid(W_g x)_h, W_g [heads, hidden], x the mixer's input
+    # The values are the keys as projected (before QK-norm and the position encoding): there is no value matrix, and
+    # the value heads have the keys' size.
+    values_are_keys: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -80,7 +88,7 @@ class AttentionSpec:
     def general(self) -> bool:
         """Whether the layer needs what only the general attention kernels compute."""
         return bool(self.v_head_dim not in (None, self.head_dim) or self.softcap or self.distance_bias or self.keep_first
-                    or self.sink or self.gate)
+                    or self.sink or self.gate or self.values_are_keys or getattr(self.position, "interleaved", False))
 
 
 @dataclass(frozen=True)
@@ -120,6 +128,62 @@ class GatedLinearAttentionSpec:
     tau: float
     norm_eps: float
     kind: str = "gated_linear_attention"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class DecayedLinearAttentionSpec:
+    """Linear attention with one constant decay per head: S <- decay_h S + k v^T, o = S^T (q_scale q), per head.
+
+    q, k [heads x key_dim] and v [heads x value_dim] pass ``activation`` ("silu" or None) after their products. The
+    read-out is RMS-normed, over all heads together when ``whole_norm`` (weight [heads * value_dim]), else per head
+    (weight [value_dim] shared by the heads), and multiplied by ``gate_activation`` ("sigmoid" or "silu") of W_g x
+    before the output product. The state is float32 and starts at zero."""
+
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]
+    norm_eps: float
+    activation: Optional[str] = "silu"
+    whole_norm: bool = True
+    gate_activation: str = "sigmoid"
+    q_scale: float = 1.0
+    kind: str = "decayed_linear_attention"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec:
+    """Several mixers side by side that read the same input; the result is the sum of ``scale_i * mixer_i(x)``.
+
+    ``branches``: (prefix of the branch's tensors inside the mixer, the branch's spec, its scale). Each branch keeps
+    the cache its kind needs. The branches' input matrices are stacked into one product and so are their output
+    matrices (the scales ride on the activations), so the branches cost two products together."""
+
+    hidden_size: int
+    branches: Tuple[Tuple[str, Any, float], ...]
+    kind: str = "parallel_mixer"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of SwiGLU experts W_down (silu(W_gate x) * (W_up x)), ``top`` per token.
+
+    The router has ``num_experts + num_identity`` outputs; the last ``num_identity`` are experts without tensors
+    that return their input. Scores are a softmax over all outputs (float32); the choice goes by score plus a
+    learned correction, among the outputs of the ``keep_groups`` best of ``groups`` equal groups of neighbours (a
+    group's score is its largest choice score); the weights are the chosen outputs' plain scores over their sum."""
+
+    hidden_size: int
+    intermediate_size: int
+    num_experts: int
+    num_identity: int
+    top: int
+    groups: int = 1
+    keep_groups: int = 1
+    kind: str = "routed_experts"
     names: Mapping[str, str] = field(default_factory=dict)
 
 
@@ -174,6 +238,11 @@ class LayerSpec:
     mixer_norm_name: str
     ffn_norm_name: Optional[str]
     arrangement: str = "pre_norm"
+    # What the "parallel" arrangement adds: h += residual_multiplier * (mixer_scale * mixer(n) + ffn_scale * ffn(n))
+    # with ONE norm n = mixer_norm(h) that both sublayers read; the two scales are tensors [hidden] (None: ones).
+    residual_multiplier: float = 1.0
+    mixer_scale_name: Optional[str] = None
+    ffn_scale_name: Optional[str] = None
 
 
 @dataclass(frozen=True)

@@ -5,7 +5,9 @@
 //
 // Token i of a request sees key j iff j <= i and (window == 0 or i - j < window or j < keep_first). For head h:
 //   s_j = (q . k_j) * scale;  s_j <- cap * tanh(s_j / cap) if cap > 0;  s_j <- s_j - r1_h * ln(1 + r2_h * (i - j)) if r1;
-//   p_j = exp(s_j) / (sink + sum_j' exp(s_j'));  out = sigmoid(gate_h) * sum_j p_j v_j.
+//   p_j = exp(s_j) / (sink + sum_j' exp(s_j'));  out = out_scale * sigmoid(gate_h) * sum_j p_j v_j.
+// The sink is exp(0), or exp(sinks[h]) where a learned logit per head is given. The output's rows have a pitch of
+// their own (ldo elements), so a layer may write its heads into a part of a wider row.
 // Scores, weights and sums are float32. The visible keys are walked in tiles of kTile keys whose borders are
 // multiples of kTile counted from position 0 (the kept first tokens come first), so what a token computes, and in
 // which order, depends on its position only: not on how the prompt was cut or on what else is in the batch.
@@ -18,15 +20,19 @@ namespace {
 constexpr int kTile = 128;    // keys per tile = threads per block
 constexpr int kMaxGroup = 16;  // query heads of a key/value head that one block serves at a time
 
-// One block per token: RMSNorm of every head of q and k over D with a plain weight (or none), the normed q to
-// q_out [N, H * D], the normed k and v into the pages at the token's (page, offset).
+// One block per token: RMSNorm of every head of q and k over D with a plain weight (or none), then (where tables are
+// given) the rotation of the first `rot` channels of each head by the token's angles, channel 2i with 2i + 1
+// (interleaved) or i with i + rot / 2; q to q_out [N, H * D], k and the untouched v into the pages at the token's
+// (page, offset). v may be the very rows of k: the values are then the keys as projected, before the rotation.
 template <typename T>
 __global__ void qk_norm_store_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk,
                                      const T* __restrict__ v, long long ldv, const float* __restrict__ qw,
                                      const float* __restrict__ kw, float eps, T* __restrict__ q_out,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ block_table,
                                      int max_blocks, const int* __restrict__ seq_of_token,
-                                     const int* __restrict__ positions, int page_size, int H, int G, int D, int V, int write) {
+                                     const int* __restrict__ positions, int page_size, int H, int G, int D, int V, int write,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
+                                     int interleaved) {
   const int n = blockIdx.x;
   const int req = seq_of_token[n];
   if (req < 0) return;
@@ -48,7 +54,20 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ q, long long ldq, con
     }
     T* dst = is_q ? q_out + ((size_t)n * H + head) * D
                   : k_pool + (((size_t)page * G + (head - H)) * page_size + off) * D;
-    for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(w != nullptr ? to_f32(src[d]) * inv * w[d] : to_f32(src[d]));
+    if (cos_t == nullptr) {
+      for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(w != nullptr ? to_f32(src[d]) * inv * w[d] : to_f32(src[d]));
+      continue;
+    }
+    const int half = rot / 2;
+    for (int i = lane; i < half; i += 32) {
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+      float u = to_f32(src[a]), x = to_f32(src[b]);
+      if (w != nullptr) { u *= inv * w[a]; x *= inv * w[b]; }
+      const float c = cos_t[(size_t)n * half + i], sn = sin_t[(size_t)n * half + i];
+      dst[a] = from_f32<T>(fmaf(u, c, -x * sn));
+      dst[b] = from_f32<T>(fmaf(x, c, u * sn));
+    }
+    for (int d = rot + lane; d < D; d += 32) dst[d] = from_f32<T>(w != nullptr ? to_f32(src[d]) * inv * w[d] : to_f32(src[d]));
   }
   if (write) {
     for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
@@ -97,7 +116,8 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_of_token,
                          const int* __restrict__ positions, T* __restrict__ out, float scale, int window, int keep_first,
                          float cap, const float* __restrict__ r1, const float* __restrict__ r2, int sink,
-                         const TG* __restrict__ gate, long long ldg, int page_size, int H, int G, int D, int V, int row_words) {
+                         const TG* __restrict__ gate, long long ldg, int page_size, int H, int G, int D, int V, int row_words,
+                         const float* __restrict__ sinks, float out_scale, long long ldo) {
   extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x, g = blockIdx.y;
   const int req = seq_of_token[n];
@@ -122,7 +142,10 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
       qs[i] = to_f32(q[((size_t)n * H + (size_t)g * group + h0) * D + i]);
     float m_run[kMaxGroup], l_run[kMaxGroup];
 #pragma unroll
-    for (int a = 0; a < kMaxGroup; ++a) { m_run[a] = sink ? 0.f : -INFINITY; l_run[a] = sink ? 1.f : 0.f; }
+    for (int a = 0; a < kMaxGroup; ++a) {
+      m_run[a] = sinks != nullptr ? sinks[g * group + h0 + min(a, heads - 1)] : sink ? 0.f : -INFINITY;
+      l_run[a] = sinks != nullptr || sink ? 1.f : 0.f;
+    }
     // running sums of value channel c = tid + kTile * i for every head: kept in shared memory (any V), thread-private
     float* acc = stat + kMaxGroup * 2;  // [kMaxGroup][Vp], Vp = V rounded up to kTile
     const int Vp = (V + kTile - 1) / kTile * kTile;
@@ -220,7 +243,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
           const int h = g * group + h0 + a;
           float o = l_run[a] > 0.f ? acc[a * Vp + c] / l_run[a] : 0.f;
           if (gate != nullptr) o *= 1.f / (1.f + expf(-to_f32(gate[(size_t)n * ldg + h])));
-          out[((size_t)n * H + h) * V + c] = from_f32<T>(o);
+          out[(size_t)n * ldo + (size_t)h * V + c] = from_f32<T>(o * out_scale);
         }
       }
     }
@@ -232,22 +255,25 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
 AKAS_API int akas_qk_norm_store(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
                                 const float* qw, const float* kw, float eps, void* q_out, void* k_pool, void* v_pool,
                                 const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
-                                int page_size, int N, int H, int G, int D, int V, int write, int dtype, cudaStream_t stream) {
+                                int page_size, int N, int H, int G, int D, int V, int write, int dtype, const float* cos_t,
+                                const float* sin_t, int rot, int interleaved, cudaStream_t stream) {
   if (N <= 0) return 0;
+  if (cos_t != nullptr && (rot <= 0 || rot % 2 || rot > D)) return (int)cudaErrorInvalidValue;
   if (dtype == AKAS_F32)
     return launch_ordinary(qk_norm_store_kernel<float>, dim3(N), dim3(128), 0, stream, (const float*)q, ldq, (const float*)k, ldk,
                           (const float*)v, ldv, qw, kw, eps, (float*)q_out, (float*)k_pool, (float*)v_pool, block_table,
-                          max_blocks, seq_of_token, positions, page_size, H, G, D, V, write);
+                          max_blocks, seq_of_token, positions, page_size, H, G, D, V, write, cos_t, sin_t, rot, interleaved);
   return launch_ordinary(qk_norm_store_kernel<bf16>, dim3(N), dim3(128), 0, stream, (const bf16*)q, ldq, (const bf16*)k, ldk,
                         (const bf16*)v, ldv, qw, kw, eps, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks,
-                        seq_of_token, positions, page_size, H, G, D, V, write);
+                        seq_of_token, positions, page_size, H, G, D, V, write, cos_t, sin_t, rot, interleaved);
 }
 
 template <typename T, typename TG>
 static int launch_general(const void* q, const void* k_pool, const void* v_pool, const int* block_table, int max_blocks,
                           const int* seq_of_token, const int* positions, void* out, float scale, int window, int keep_first,
                           float cap, const float* r1, const float* r2, int sink, const void* gate, long long ldg,
-                          int page_size, int N, int H, int G, int D, int V, cudaStream_t stream) {
+                          int page_size, int N, int H, int G, int D, int V, const float* sinks, float out_scale,
+                          long long ldo, cudaStream_t stream) {
   const int Vp = (V + kTile - 1) / kTile * kTile;
   const int row_words = (kMaxGroup * D + kMaxGroup * kTile + kMaxGroup * 4 + kMaxGroup * 2 + kMaxGroup * Vp + 1) / 2 * 2;
   const size_t smem = sizeof(float) * (size_t)row_words + sizeof(long long) * kTile;
@@ -262,19 +288,19 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
   }
   return launch_ordinary(attention_general_kernel<T, TG>, dim3(N, G), dim3(kTile), smem, stream, (const T*)q, (const T*)k_pool,
                         (const T*)v_pool, block_table, max_blocks, seq_of_token, positions, (T*)out, scale, window, keep_first,
-                        cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words);
+                        cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words, sinks, out_scale, ldo);
 }
 
 AKAS_API int akas_attention_general(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                                     int max_blocks, const int* seq_of_token, const int* positions, void* out, float scale,
                                     int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                     const void* gate, long long ldg, int page_size, int N, int H, int G, int D, int V,
-                                    int dtype, cudaStream_t stream) {
+                                    int dtype, const float* sinks, float out_scale, long long ldo, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (G <= 0 || H % G) return (int)cudaErrorInvalidValue;
   if (dtype == AKAS_F32)
     return launch_general<float, float>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
-                                        keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, stream);
+                                        keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, stream);
   return launch_general<bf16, bf16>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
-                                    keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, stream);
+                                    keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, stream);
 }

@@ -7,8 +7,9 @@
 // come from the pages by 16-byte cp.async copies, two tiles in flight; columns beyond the real head sizes (which need
 // only be multiples of 8) are zero in shared memory. S = Q.K^T and O += P.V are mma.sync m16n8k16; between them, in
 // float32 registers: scale, cap * tanh(s / cap), minus r1 * ln(1 + r2 * distance), the mask by absolute positions,
-// and the running maximum and sum, which start at 0 and 1 where the softmax has a sink. The head's output is
-// multiplied by sigmoid(gate) on its way out.
+// and the running maximum and sum, which start at the sink's logit (0, or a learned number per head) and 1 where the
+// softmax has a sink. The head's output is multiplied by sigmoid(gate) and by a constant on its way out, into rows
+// whose pitch is the caller's.
 //
 // Packed launches serve steps of single tokens (decoding): a block's rows are then the query heads that share one
 // key/value head, all at the token's position, so its keys and values are read once for the whole group; warps
@@ -45,6 +46,9 @@ struct Options {
   int window, keep_first, sink;
   const bf16* gate;
   long long ldg;
+  const float* sinks;  // a learned sink logit per head, or null
+  float out_scale;
+  long long ldo;       // elements between the output rows of two tokens
 };
 
 constexpr int kTableBefore = 128, kTableAfter = 192;  // entries of the penalty table on either side of the window's distances
@@ -133,12 +137,14 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   for (int nb = 0; nb < NB; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
   // running maximum (in units of log2 e) and this thread's share of the running sum; the sink is a term exp(0)
   float m_run[2], l_run[2];
-  m_run[0] = m_run[1] = opt.sink ? 0.f : -INFINITY;
-  l_run[0] = l_run[1] = opt.sink && t == 0 ? 1.f : 0.f;
   const int row2[2] = {warp * 16 + g, warp * 16 + g + 8};
   const int qpos[2] = {packed ? pos0 : pos0 + row2[0], packed ? pos0 : pos0 + row2[1]};
   const int head2[2] = {packed ? kvh * group + min(row2[0], rows - 1) : (int)blockIdx.x,
                         packed ? kvh * group + min(row2[1], rows - 1) : (int)blockIdx.x};
+  const bool sunk = opt.sink || opt.sinks != nullptr;
+  m_run[0] = opt.sinks != nullptr ? opt.sinks[head2[0]] * kLog2e : opt.sink ? 0.f : -INFINITY;
+  m_run[1] = opt.sinks != nullptr ? opt.sinks[head2[1]] * kLog2e : opt.sink ? 0.f : -INFINITY;
+  l_run[0] = l_run[1] = sunk && t == 0 ? 1.f : 0.f;
   const bool biased = opt.r1 != nullptr;
   // r1 ln(1 + r2 d) in units of log2 e is r1 lg2(1 + r2 d): the two factors ln 2 and log2 e cancel
   const float r1[2] = {biased ? opt.r1[head2[0]] : 0.f, biased ? opt.r1[head2[1]] : 0.f};
@@ -269,7 +275,8 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     float inv = l_run[h2] > 0.f ? 1.f / l_run[h2] : 0.f;
     const size_t token = packed ? q0 : q0 + row;
     if (opt.gate != nullptr) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[token * opt.ldg + head2[h2]])));
-    bf16* dst = out + (token * H + head2[h2]) * V;
+    inv *= opt.out_scale;
+    bf16* dst = out + token * opt.ldo + (size_t)head2[h2] * V;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
       if (nb * 8 + 2 * t < V)
@@ -312,12 +319,14 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
                                        int max_blocks, const int* cu_seqlens, const int* positions, void* out, float scale,
                                        int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                        const void* gate, long long ldg, int page_size, int tiles, int H, int KH, int D, int V,
-                                       int R, int packed, cudaStream_t stream) {
+                                       int R, int packed, const float* sinks, float out_scale, long long ldo,
+                                       cudaStream_t stream) {
   if (!akas_attention_general_tc_takes(D, V)) return 3999;
+  if (ldo % 2) return 3999;
   if (packed && (KH <= 0 || H / KH > BQ || tiles != R)) return 3999;
   if (KH <= 0 || H % KH || tiles > 65535 || R <= 0) return (int)cudaErrorInvalidValue;
   if (tiles <= 0) return 0;
-  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, (const bf16*)gate, ldg};
+  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, (const bf16*)gate, ldg, sinks, out_scale, ldo};
   const int dk = (D + 31) / 32, dv = (V + 31) / 32;
 #define AKAS_TC(A, B)                                                                                                   \
   if (dk == A && dv == B)                                                                                               \

@@ -258,6 +258,44 @@ AKAS_API int akas_add_rows(float* h, const void* table, const int* index, int N,
   return launch_ordinary(add_rows_kernel<bf16>, dim3(N), dim3(threads), 0, stream, h, (const bf16*)table, index, C);
 }
 
+// x[n, c] += mult * (ls_a[c] * a[n, c] + ls_b[c] * b[n, c]) in place on the float32 residual stream: the update of a
+// block whose sublayers all read one norm of x and whose results meet, each through a learned scale per channel,
+// in one sum. b (and ls_b) may be null: a block without the second sublayer. Four channels a thread where C allows.
+__global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ ls_a,
+                                  const float* __restrict__ b, const float* __restrict__ ls_b, float mult, long long total,
+                                  int C, int vec) {
+  const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * (vec ? 4 : 1);
+  if (i >= total) return;
+  if (vec) {
+    const int c = (int)(i % C);
+    float4 xv = *reinterpret_cast<float4*>(x + i);
+    const float4 av = *reinterpret_cast<const float4*>(a + i), la = *reinterpret_cast<const float4*>(ls_a + c);
+    float4 sum = make_float4(la.x * av.x, la.y * av.y, la.z * av.z, la.w * av.w);
+    if (b != nullptr) {
+      const float4 bv = *reinterpret_cast<const float4*>(b + i), lb = *reinterpret_cast<const float4*>(ls_b + c);
+      sum.x = fmaf(lb.x, bv.x, sum.x); sum.y = fmaf(lb.y, bv.y, sum.y); sum.z = fmaf(lb.z, bv.z, sum.z); sum.w = fmaf(lb.w, bv.w, sum.w);
+    }
+    xv.x = fmaf(mult, sum.x, xv.x); xv.y = fmaf(mult, sum.y, xv.y); xv.z = fmaf(mult, sum.z, xv.z); xv.w = fmaf(mult, sum.w, xv.w);
+    *reinterpret_cast<float4*>(x + i) = xv;
+  } else {
+    const int c = (int)(i % C);
+    float sum = ls_a[c] * a[i];
+    if (b != nullptr) sum = fmaf(ls_b[c], b[i], sum);
+    x[i] = fmaf(mult, sum, x[i]);
+  }
+}
+
+AKAS_API int akas_scaled_add(float* x, const float* a, const float* ls_a, const float* b, const float* ls_b, float mult, int N,
+                             int C, cudaStream_t stream) {
+  const long long total = (long long)N * C;
+  if (total <= 0) return 0;
+  const bool aligned = ((uintptr_t)x | (uintptr_t)a | (uintptr_t)ls_a | (uintptr_t)b | (uintptr_t)ls_b) % 16 == 0;
+  const int vec = C % 4 == 0 && aligned;
+  const long long threads = vec ? total / 4 : total;
+  return launch_ordinary(scaled_add_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream, x, a, ls_a, b, ls_b,
+                         mult, total, C, vec);
+}
+
 // PolyNorm of rows: out = a N(z) + b N(z^2) + c N(z^3) + e with N(x) = x / sqrt(mean(x^2) + eps) over the row and
 // the powers taken element by element; coeffs = (a, b, c, e). One block per row; powers and sums are float32. VEC: the
 // row's width is a multiple of 8 and rows start on 16 bytes, so 8 elements move at a time.

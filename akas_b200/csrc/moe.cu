@@ -1,0 +1,257 @@
+// A routed feed-forward (mixture of experts): the router, and the experts for steps of few tokens and for float32.
+//
+// Router, per token, all in float32: logits z = W_r h over the R router outputs (one chain of sums per (token,
+// output) whose order depends on the width only), s = softmax(z); the choice score is s + correction; the outputs
+// form `groups` equal groups of neighbours, a group's score is its largest choice score, only outputs of the `keep`
+// best groups can be chosen; the `top` largest choice scores among those are chosen (ties: the lower index); the
+// weights are the chosen outputs' s over their sum (+ 1e-20). Router outputs from `experts` on are identity experts:
+// they have no matrices and return their input.
+//
+// Experts, token by token (moe_gate_up, moe_down): act[pair] = silu(W_gate h) * (W_up h) for every (token, chosen
+// real expert) pair, then out[n] = sum over the token's chosen outputs of weight * (W_down act, or h for an identity
+// expert), added in the order of the choice. Every output is one warp's sum over the inner size in a fixed order, so
+// a token's result does not depend on what else the step holds. Weights of all experts are stacked: gate and up as
+// [experts, 2 F, C] (gate rows first), down as [experts, C, F].
+#include "common.cuh"
+
+using namespace akas;
+
+namespace {
+
+constexpr int kRouteTokens = 8;   // tokens of a router block = its warps
+constexpr int kRouteChunk = 512;  // channels of h staged at a time
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(kRouteTokens * 32)
+moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ w, const float* __restrict__ correction,
+                 int* __restrict__ chosen, float* __restrict__ weights, int N, int C, int R, int groups, int keep, int top) {
+  extern __shared__ float smem[];
+  float* rows = smem;                              // [kRouteTokens][kRouteChunk]
+  float* z = rows + kRouteTokens * kRouteChunk;    // [kRouteTokens][R] logits, then scores
+  float* pick = z + kRouteTokens * R;              // [kRouteTokens][R] choice scores
+  float* gbest = pick + kRouteTokens * R;          // [kRouteTokens][groups]
+  const int n0 = blockIdx.x * kRouteTokens;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kRouteTokens * R; i += blockDim.x) z[i] = 0.f;
+  for (int c0 = 0; c0 < C; c0 += kRouteChunk) {
+    const int width = min(kRouteChunk, C - c0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < kRouteTokens * width; i += blockDim.x) {
+      const int t = i / width, c = i % width;
+      rows[t * kRouteChunk + c] = n0 + t < N ? to_f32(h[(size_t)(n0 + t) * ldh + c0 + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int e = warp; e < R; e += kRouteTokens) {
+      float acc[kRouteTokens];
+#pragma unroll
+      for (int t = 0; t < kRouteTokens; ++t) acc[t] = 0.f;
+      for (int c = lane; c < width; c += 32) {
+        const float wv = w[(size_t)e * C + c0 + c];
+#pragma unroll
+        for (int t = 0; t < kRouteTokens; ++t) acc[t] = fmaf(rows[t * kRouteChunk + c], wv, acc[t]);
+      }
+#pragma unroll
+      for (int t = 0; t < kRouteTokens; ++t) {
+        const float sum = warp_sum(acc[t]);
+        if (lane == 0) z[t * R + e] += sum;
+      }
+    }
+  }
+  __syncthreads();
+  // warp t chooses for token n0 + t
+  const int n = n0 + warp;
+  if (n >= N) return;
+  float* zt = z + warp * R;
+  float* pt = pick + warp * R;
+  float* gt = gbest + warp * groups;
+  float top_z = -INFINITY;
+  for (int e = lane; e < R; e += 32) top_z = fmaxf(top_z, zt[e]);
+  top_z = warp_max(top_z);
+  float sum = 0.f;
+  for (int e = lane; e < R; e += 32) {
+    const float p = expf(zt[e] - top_z);
+    zt[e] = p;
+    sum += p;
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  for (int e = lane; e < R; e += 32) {
+    zt[e] *= inv;
+    pt[e] = zt[e] + correction[e];
+  }
+  __syncwarp();
+  const int size = R / groups;
+  if (groups > 1 && keep < groups) {
+    for (int g = lane; g < groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * size; e < (g + 1) * size; ++e) best = fmaxf(best, pt[e]);
+      gt[g] = best;
+    }
+    __syncwarp();
+    // a group stays iff fewer than `keep` groups beat it (a tie goes to the lower index)
+    for (int g = lane; g < groups; g += 32) {
+      int ahead = 0;
+      for (int o = 0; o < groups; ++o) ahead += gt[o] > gt[g] || (gt[o] == gt[g] && o < g);
+      if (ahead >= keep)
+        for (int e = g * size; e < (g + 1) * size; ++e) pt[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < R; e += 32)
+      if (pt[e] > best) { best = pt[e]; at = e; }  // ascending e: the first of equal scores stays
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at == 0x7fffffff) at = 0;  // fewer choosable outputs than `top`: cannot happen for a valid configuration
+    if (lane == 0) {
+      chosen[(size_t)n * top + k] = at;
+      weights[(size_t)n * top + k] = zt[at];
+      pt[at] = -INFINITY;
+    }
+    total += zt[at];
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float norm = 1.f / (total + 1e-20f);
+    for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] *= norm;
+  }
+}
+
+// One warp per (pair, hidden channel f): both dots over C, act = silu(gate) * up. Pairs of identity experts do nothing.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gate_up_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_gate_up, const int* __restrict__ chosen,
+                   T* __restrict__ act, int pairs, int top, int C, int F, int experts) {
+  const int pair = blockIdx.x;
+  const int e = chosen[pair];
+  if (e >= experts || e < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const T* x = h + (size_t)(pair / top) * ldh;
+  const T* wg = w_gate_up + (size_t)e * 2 * F * C;
+  constexpr int N = Vec<T>::N;
+  const bool vec = C % N == 0 && ldh % N == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)w_gate_up % 16) == 0;
+  for (int f = blockIdx.y * warps + warp; f < F; f += gridDim.y * warps) {
+    const T* g_row = wg + (size_t)f * C;
+    const T* u_row = wg + (size_t)(F + f) * C;
+    float ag = 0.f, au = 0.f;
+    if (vec) {
+      for (int c = lane * N; c < C; c += 32 * N) {
+        float xv[N], gv[N], uv[N];
+        load_vec(x + c, xv);
+        load_vec(g_row + c, gv);
+        load_vec(u_row + c, uv);
+#pragma unroll
+        for (int i = 0; i < N; ++i) { ag = fmaf(xv[i], gv[i], ag); au = fmaf(xv[i], uv[i], au); }
+      }
+    } else {
+      for (int c = lane; c < C; c += 32) {
+        const float xv = to_f32(x[c]);
+        ag = fmaf(xv, to_f32(g_row[c]), ag);
+        au = fmaf(xv, to_f32(u_row[c]), au);
+      }
+    }
+    ag = warp_sum(ag);
+    au = warp_sum(au);
+    if (lane == 0) act[(size_t)pair * F + f] = from_f32<T>(silu_f(ag) * au);
+  }
+}
+
+// One warp per (token, output channel c): the weighted sum over the token's chosen outputs.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_down_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_down, const int* __restrict__ chosen,
+                const float* __restrict__ weights, const T* __restrict__ act, float* __restrict__ out, int top, int C, int F,
+                int experts) {
+  const int n = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  constexpr int N = Vec<T>::N;
+  const bool vec = F % N == 0 && ((uintptr_t)act % 16) == 0 && ((uintptr_t)w_down % 16) == 0;
+  for (int c = blockIdx.y * warps + warp; c < C; c += gridDim.y * warps) {
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int e = chosen[(size_t)n * top + k];
+      const float g = weights[(size_t)n * top + k];
+      if (e >= experts) {
+        total = fmaf(g, to_f32(h[(size_t)n * ldh + c]), total);
+        continue;
+      }
+      const T* row = w_down + ((size_t)e * C + c) * F;
+      const T* a = act + ((size_t)n * top + k) * F;
+      float acc = 0.f;
+      if (vec) {
+        for (int f = lane * N; f < F; f += 32 * N) {
+          float av[N], wv[N];
+          load_vec(a + f, av);
+          load_vec(row + f, wv);
+#pragma unroll
+          for (int i = 0; i < N; ++i) acc = fmaf(av[i], wv[i], acc);
+        }
+      } else {
+        for (int f = lane; f < F; f += 32) acc = fmaf(to_f32(a[f]), to_f32(row[f]), acc);
+      }
+      total = fmaf(g, warp_sum(acc), total);
+    }
+    if (lane == 0) out[(size_t)n * C + c] = total;
+  }
+}
+
+}  // namespace
+
+AKAS_API int akas_moe_route(const void* h, long long ldh, const float* w, const float* correction, int* chosen, float* weights,
+                            int N, int C, int R, int groups, int keep, int top, int dtype, cudaStream_t stream) {
+  if (N <= 0) return 0;
+  if (R <= 0 || groups <= 0 || R % groups || keep <= 0 || keep > groups || top <= 0 || top > keep * (R / groups))
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = sizeof(float) * ((size_t)kRouteTokens * kRouteChunk + 2 * (size_t)kRouteTokens * R + (size_t)kRouteTokens * groups);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  const dim3 grid((N + kRouteTokens - 1) / kRouteTokens);
+  static size_t allowed[64][2] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  const int which = dtype == AKAS_F32 ? 0 : 1;
+  if (smem > 48 * 1024 && device < 64 && allowed[device][which] < smem) {
+    const cudaError_t e = which == 0
+        ? cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+        : cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    allowed[device][which] = smem;
+  }
+  if (dtype == AKAS_F32)
+    return launch_ordinary(moe_route_kernel<float>, grid, dim3(kRouteTokens * 32), smem, stream, (const float*)h, ldh, w,
+                           correction, chosen, weights, N, C, R, groups, keep, top);
+  return launch_ordinary(moe_route_kernel<bf16>, grid, dim3(kRouteTokens * 32), smem, stream, (const bf16*)h, ldh, w, correction,
+                         chosen, weights, N, C, R, groups, keep, top);
+}
+
+AKAS_API int akas_moe_gate_up(const void* h, long long ldh, const void* w_gate_up, const int* chosen, void* act, int N,
+                              int top, int C, int F, int experts, int dtype, cudaStream_t stream) {
+  if (N <= 0 || top <= 0 || experts <= 0) return 0;
+  const int pairs = N * top;
+  const dim3 grid(pairs, max(1, min((F + 7) / 8, pairs >= 4096 ? 2 : 16)));
+  if (dtype == AKAS_F32)
+    return launch_ordinary(moe_gate_up_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, ldh, (const float*)w_gate_up,
+                           chosen, (float*)act, pairs, top, C, F, experts);
+  return launch_ordinary(moe_gate_up_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, ldh, (const bf16*)w_gate_up,
+                         chosen, (bf16*)act, pairs, top, C, F, experts);
+}
+
+AKAS_API int akas_moe_down(const void* h, long long ldh, const void* w_down, const int* chosen, const float* weights,
+                           const void* act, float* out, int N, int top, int C, int F, int experts, int dtype,
+                           cudaStream_t stream) {
+  if (N <= 0) return 0;
+  const dim3 grid(N, max(1, min((C + 7) / 8, N >= 2048 ? 2 : 32)));
+  if (dtype == AKAS_F32)
+    return launch_ordinary(moe_down_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, ldh, (const float*)w_down, chosen,
+                           weights, (const float*)act, out, top, C, F, experts);
+  return launch_ordinary(moe_down_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, ldh, (const bf16*)w_down, chosen,
+                         weights, (const bf16*)act, out, top, C, F, experts);
+}

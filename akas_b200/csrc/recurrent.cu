@@ -60,6 +60,8 @@ __global__ void decay_gates_kernel(const T* __restrict__ low, long long ld, cons
 // their partial sums by shuffles. The step's tokens come through shared memory in chunks of CH (fewer where rows are long).
 //
 //   GLA:    s <- alpha_t[kk] s + k_t[kk] v_t[j];                                  o_t[j] = sum_kk s q_t[kk]
+//   FIXED:  the same with one constant decay per head in place of alpha_t[kk] (decay [H]); with `act`, q, k and v
+//           pass silu on their way in (the mixer's activations, applied in float32).
 //   DELTA:  s <- g_t s; u = beta_t (v_t[j] - sum_kk s k_t[kk]); s <- s + k_t[kk] u; o_t[j] = sum_kk s q_t[kk]
 constexpr int kPad = 4;  // floats between the R-blocks of a shared row: neighbouring lanes' 16-byte reads miss each other's banks
 
@@ -69,18 +71,18 @@ template <int KS> __device__ __forceinline__ float group_sum(float v) {
   return v;
 }
 
-template <typename T, int R, int KS, int CH, int TH, bool DELTA>
+template <typename T, int R, int KS, int CH, int TH, bool DELTA, bool FIXED = false>
 __global__ void __launch_bounds__(TH)
 scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk, const T* __restrict__ v,
             long long ldv, const float* __restrict__ decay /* GLA: alpha [N, H * D]; DELTA: g [N, H] */,
             const float* __restrict__ beta /* DELTA: [N, H] */, float* __restrict__ state, long long slot_stride,
             const int* __restrict__ cu_seqlens, const int* __restrict__ slots, float* __restrict__ out, int H, int rep,
-            int D, int V, float q_scale, int write) {
+            int D, int V, float q_scale, int write, int act) {
   constexpr int VT = TH / KS;           // value channels of a block
   constexpr int ROW = KS * (R + kPad);  // floats of a padded shared row of key channels
   __shared__ __align__(16) float sq[CH][ROW];
   __shared__ __align__(16) float sk[CH][ROW];
-  __shared__ __align__(16) float sa[DELTA ? 1 : CH][DELTA ? 4 : ROW];
+  __shared__ __align__(16) float sa[DELTA || FIXED ? 1 : CH][DELTA || FIXED ? 4 : ROW];
   __shared__ float sv[CH][VT];
   __shared__ float sg[CH], sb[CH];
 
@@ -112,7 +114,8 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
   // when that is done: the recurrence never waits for global memory except at its first chunk.
   constexpr int NQ = (CH * KS * R + TH - 1) / TH, NV = (CH * VT + TH - 1) / TH;
   T rq[NQ], rk[NQ], rv[NV];  // as fetched: widening them here would make the loop below wait for the loads at once
-  float ra[DELTA ? 1 : NQ], rg = 0.f, rb = 0.f;
+  float ra[DELTA || FIXED ? 1 : NQ], rg = 0.f, rb = 0.f;
+  const float fixed = FIXED ? decay[h] : 0.f;
   const T zero = from_f32<T>(0.f);
   auto fetch = [&](int c0) {
     const int count = min(CH, t_end - c0);
@@ -124,7 +127,7 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
       const size_t n = (size_t)(c0 + t);
       rq[u] = in ? q[n * ldq + (size_t)hk * D + kk] : zero;
       rk[u] = in ? k[n * ldk + (size_t)hk * D + kk] : zero;
-      if (!DELTA) ra[u] = in ? decay[n * ((size_t)H * D) + (size_t)h * D + kk] : 0.f;
+      if (!DELTA && !FIXED) ra[u] = in ? decay[n * ((size_t)H * D) + (size_t)h * D + kk] : 0.f;
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
@@ -147,15 +150,21 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
       if (i < CH * KS * R) {
         const int t = i / (KS * R), kk = i % (KS * R);
         const int at = kk + (kk / R) * kPad;
-        sq[t][at] = to_f32(rq[u]) * q_scale;
-        sk[t][at] = to_f32(rk[u]);
-        if (!DELTA) sa[t][at] = ra[u];
+        float qv = to_f32(rq[u]), kv = to_f32(rk[u]);
+        if (FIXED && act) { qv *= sigmoid_f(qv); kv *= sigmoid_f(kv); }
+        sq[t][at] = qv * q_scale;
+        sk[t][at] = kv;
+        if (!DELTA && !FIXED) sa[t][at] = ra[u];
       }
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
       const int i = threadIdx.x + u * TH;
-      if (i < CH * VT) sv[i / VT][i % VT] = to_f32(rv[u]);
+      if (i < CH * VT) {
+        float vv = to_f32(rv[u]);
+        if (FIXED && act) vv *= sigmoid_f(vv);
+        sv[i / VT][i % VT] = vv;
+      }
     }
     if (DELTA && threadIdx.x < CH) {
       sg[threadIdx.x] = rg;
@@ -188,6 +197,15 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
           s[r + 2] = fmaf(kv.z, u, s[r + 2]); s[r + 3] = fmaf(kv.w, u, s[r + 3]);
           acc = fmaf(s[r], qv.x, acc); acc2 = fmaf(s[r + 1], qv.y, acc2); acc = fmaf(s[r + 2], qv.z, acc); acc2 = fmaf(s[r + 3], qv.w, acc2);
         }
+      } else if (FIXED) {
+#pragma unroll
+        for (int r = 0; r < R; r += 4) {
+          const float4 kv = *reinterpret_cast<const float4*>(kr + r);
+          const float4 qv = *reinterpret_cast<const float4*>(qr + r);
+          s[r] = fmaf(fixed, s[r], kv.x * vj); s[r + 1] = fmaf(fixed, s[r + 1], kv.y * vj);
+          s[r + 2] = fmaf(fixed, s[r + 2], kv.z * vj); s[r + 3] = fmaf(fixed, s[r + 3], kv.w * vj);
+          acc = fmaf(s[r], qv.x, acc); acc2 = fmaf(s[r + 1], qv.y, acc2); acc = fmaf(s[r + 2], qv.z, acc); acc2 = fmaf(s[r + 3], qv.w, acc2);
+        }
       } else {
         const float* ar = &sa[t][ks * (R + kPad)];
 #pragma unroll
@@ -218,10 +236,11 @@ scan_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, lon
   }
 }
 
-template <typename T, bool DELTA>
+template <typename T, bool DELTA, bool FIXED = false>
 int launch_scan(const T* q, long long ldq, const T* k, long long ldk, const T* v, long long ldv, const float* decay,
                 const float* beta, float* state, long long slot_stride, const int* cu_seqlens, const int* slots, float* out,
-                int tokens, int requests, int H, int rep, int D, int V, float q_scale, int write, cudaStream_t stream) {
+                int tokens, int requests, int H, int rep, int D, int V, float q_scale, int write, cudaStream_t stream,
+                int act = 0) {
   if (requests <= 0 || H <= 0) return 0;
   if (D > 1024) return (int)cudaErrorInvalidValue;
   // (Blocks of 64 threads, which spread a head's value channels over four times as many SMs when a step holds few
@@ -231,8 +250,8 @@ int launch_scan(const T* q, long long ldq, const T* k, long long ldk, const T* v
 #define AKAS_SCAN(R, KS, CH)                                                                                              \
   {                                                                                                                       \
     const dim3 grid(H, requests, (V + 256 / KS - 1) / (256 / KS));                                                        \
-    return launch_ordinary(scan_kernel<T, R, KS, CH, 256, DELTA>, grid, dim3(256), 0, stream, q, ldq, k, ldk, v, ldv, decay,  \
-                          beta, state, slot_stride, cu_seqlens, slots, out, H, rep, D, V, q_scale, write);                \
+    return launch_ordinary(scan_kernel<T, R, KS, CH, 256, DELTA, FIXED>, grid, dim3(256), 0, stream, q, ldq, k, ldk, v, ldv,  \
+                          decay, beta, state, slot_stride, cu_seqlens, slots, out, H, rep, D, V, q_scale, write, act);    \
   }
   if (D <= 8) AKAS_SCAN(8, 1, 16)
   if (D <= 16) AKAS_SCAN(8, 2, 16)
@@ -360,32 +379,37 @@ __global__ void delta_prep_kernel(float* __restrict__ y, long long ldy, int G, i
 
 // ------------------------------------------------------------------------------------------------ gated RMS norm
 //
-// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * silu(gate).
+// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * f(gate) * out_scale, f = silu or (sigmoid != 0)
+// the sigmoid alone; the output's rows have a pitch of their own. A norm over all heads together is the call with one
+// head of H * V channels.
 template <typename TG, typename TO>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
-                                     const TG* __restrict__ gate, long long ldg, TO* __restrict__ out, int N, int H, int V) {
+                                     const TG* __restrict__ gate, long long ldg, TO* __restrict__ out, int N, int H, int V,
+                                     int sigmoid, float out_scale, long long ldo) {
   const int lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= (long long)N * H) return;
   const int n = (int)(item / H), h = (int)(item % H);
   const float* row = o + (size_t)n * H * V + (size_t)h * V;
   float ss = 0.f;
-  if (V % 4 == 0 && ldg % 4 == 0 && sizeof(TO) == sizeof(TG) && (uintptr_t)gate % (4 * sizeof(TG)) == 0) {
+  if (V % 4 == 0 && ldg % 4 == 0 && ldo % 4 == 0 && sizeof(TO) == sizeof(TG) && (uintptr_t)gate % (4 * sizeof(TG)) == 0 &&
+      (uintptr_t)out % (4 * sizeof(TO)) == 0) {
     // four channels a lane: 16-byte reads of o, 8- or 16-byte reads of the gate and writes of the result
     for (int j = lane * 4; j < V; j += 128) {
       const float4 x = *reinterpret_cast<const float4*>(row + j);
       ss = fmaf(x.x, x.x, ss); ss = fmaf(x.y, x.y, ss); ss = fmaf(x.z, x.z, ss); ss = fmaf(x.w, x.w, ss);
     }
     ss = warp_sum(ss);
-    const float inv = 1.f / sqrtf(ss / (float)V + eps);
+    const float inv = out_scale / sqrtf(ss / (float)V + eps);
     for (int j = lane * 4; j < V; j += 128) {
       const float4 x = *reinterpret_cast<const float4*>(row + j);
       const float4 wv = *reinterpret_cast<const float4*>(w + j);
       float gv[4];
       load4(gate + (size_t)n * ldg + (size_t)h * V + j, gv);
-      const float r[4] = {x.x * inv * wv.x * (gv[0] * sigmoid_f(gv[0])), x.y * inv * wv.y * (gv[1] * sigmoid_f(gv[1])),
-                          x.z * inv * wv.z * (gv[2] * sigmoid_f(gv[2])), x.w * inv * wv.w * (gv[3] * sigmoid_f(gv[3]))};
-      TO* dst = out + (size_t)n * H * V + (size_t)h * V + j;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) gv[e] = sigmoid ? sigmoid_f(gv[e]) : gv[e] * sigmoid_f(gv[e]);
+      const float r[4] = {x.x * inv * wv.x * gv[0], x.y * inv * wv.y * gv[1], x.z * inv * wv.z * gv[2], x.w * inv * wv.w * gv[3]};
+      TO* dst = out + (size_t)n * ldo + (size_t)h * V + j;
       if (sizeof(TO) == 4) {
         *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
       } else {
@@ -397,10 +421,10 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
   }
   for (int j = lane; j < V; j += 32) ss = fmaf(row[j], row[j], ss);
   ss = warp_sum(ss);
-  const float inv = 1.f / sqrtf(ss / (float)V + eps);
+  const float inv = out_scale / sqrtf(ss / (float)V + eps);
   for (int j = lane; j < V; j += 32) {
     const float gv = to_f32(gate[(size_t)n * ldg + (size_t)h * V + j]);
-    out[(size_t)n * H * V + (size_t)h * V + j] = from_f32<TO>(row[j] * inv * w[j] * (gv * sigmoid_f(gv)));
+    out[(size_t)n * ldo + (size_t)h * V + j] = from_f32<TO>(row[j] * inv * w[j] * (sigmoid ? sigmoid_f(gv) : gv * sigmoid_f(gv)));
   }
 }
 
@@ -426,6 +450,20 @@ AKAS_API int akas_gla_scan(const void* q, long long ldq, const void* k, long lon
                                      slot_stride, cu_seqlens, slots, out, tokens, requests, H, 1, D, V, q_scale, write, stream);
   return launch_scan<bf16, false>((const bf16*)q, ldq, (const bf16*)k, ldk, (const bf16*)v, ldv, alpha, nullptr, state,
                                   slot_stride, cu_seqlens, slots, out, tokens, requests, H, 1, D, V, q_scale, write, stream);
+}
+
+// The recurrence with one constant decay per head (decay [H] float32); act != 0: silu on q, k and v on their way in.
+AKAS_API int akas_decay_scan(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
+                             const float* decay, float* state, long long slot_stride, const int* cu_seqlens, const int* slots,
+                             float* out, int tokens, int requests, int H, int D, int V, float q_scale, int act, int write,
+                             int dtype, cudaStream_t stream) {
+  if (dtype == AKAS_F32)
+    return launch_scan<float, false, true>((const float*)q, ldq, (const float*)k, ldk, (const float*)v, ldv, decay, nullptr,
+                                           state, slot_stride, cu_seqlens, slots, out, tokens, requests, H, 1, D, V, q_scale,
+                                           write, stream, act);
+  return launch_scan<bf16, false, true>((const bf16*)q, ldq, (const bf16*)k, ldk, (const bf16*)v, ldv, decay, nullptr, state,
+                                        slot_stride, cu_seqlens, slots, out, tokens, requests, H, 1, D, V, q_scale, write,
+                                        stream, act);
 }
 
 AKAS_API int akas_delta_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
@@ -478,12 +516,14 @@ AKAS_API int akas_delta_prep(float* y, long long ldy, int G, int D, float q_scal
 }
 
 AKAS_API int akas_gated_rmsnorm(const float* o, const float* w, float eps, const void* gate, long long ldg, void* out, int N,
-                                int H, int V, int gate_dtype, int out_dtype, cudaStream_t stream) {
+                                int H, int V, int gate_dtype, int out_dtype, int sigmoid, float out_scale, long long ldo,
+                                cudaStream_t stream) {
   if (N <= 0 || H <= 0) return 0;
   const long long items = (long long)N * H;
   const int blocks = (int)((items + 7) / 8);
 #define AKAS_GN(TG, TO) \
-  return launch_ordinary(gated_rmsnorm_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, o, w, eps, (const TG*)gate, ldg, (TO*)out, N, H, V)
+  return launch_ordinary(gated_rmsnorm_kernel<TG, TO>, dim3(blocks), dim3(256), 0, stream, o, w, eps, (const TG*)gate, ldg, (TO*)out, N, H, V, \
+                         sigmoid, out_scale, ldo)
   if (gate_dtype == AKAS_F32 && out_dtype == AKAS_F32) AKAS_GN(float, float);
   if (gate_dtype == AKAS_F32) AKAS_GN(float, bf16);
   if (out_dtype == AKAS_F32) AKAS_GN(bf16, float);

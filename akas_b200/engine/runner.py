@@ -49,16 +49,20 @@ def default_ops(device: torch.device, dtype: torch.dtype, parts=()):
 
 
 def kernel_kinds(spec) -> tuple:
-    """The kinds of kernels that the mixers of a model ask for (``Mixer.kernels``), each once, in layer order: what is
-    compiled before the first step, and no more."""
-    from ..parts.base import mixer_class
+    """The kinds of kernels that the mixers and feed-forwards of a model ask for (``kernels(spec)`` of their classes),
+    each once, in layer order: what is compiled before the first step, and no more."""
+    from ..parts.base import ffn_class, mixer_class
 
     kinds = []
     for layer in spec.layers:
-        kernels = getattr(mixer_class(layer.mixer), "kernels", None)  # (a mixer from outside may not say: it asks for none)
-        for kind in (kernels(layer.mixer) if kernels is not None else ()):
-            if kind not in kinds:
-                kinds.append(kind)
+        asked = [(mixer_class(layer.mixer), layer.mixer)]
+        if layer.ffn is not None:
+            asked.append((ffn_class(layer.ffn), layer.ffn))
+        for cls, part in asked:
+            kernels = getattr(cls, "kernels", None)  # (a part from outside may not say: it asks for none)
+            for kind in (kernels(part) if kernels is not None else ()):
+                if kind not in kinds:
+                    kinds.append(kind)
     return tuple(kinds)
 
 

@@ -38,6 +38,15 @@ _SIGNATURES = {
         "akas_scale_cap": [c_void_p, c_float, c_float, c_longlong, c_void_p],
         "akas_add_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_polynorm": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_scaled_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
+    },
+    "moe": {
+        "akas_moe_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                           c_int, c_int, c_void_p],
+        "akas_moe_gate_up": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_void_p],
+        "akas_moe_down": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_void_p],
     },
     "recurrent": {
         "akas_decay_gates": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -50,20 +59,23 @@ _SIGNATURES = {
         "akas_delta_prep": [c_void_p, c_longlong, c_int, c_int, c_float, c_float, c_void_p, c_longlong, c_void_p, c_longlong,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_gated_rmsnorm": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                               c_void_p],
+                               c_int, c_float, c_longlong, c_void_p],
+        "akas_decay_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
+                            c_void_p],
     },
     "attention_general": {
         "akas_qk_norm_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_int, c_int, c_void_p],
+                               c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "akas_attention_general": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                    c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
-                                   c_int, c_int, c_int, c_void_p],
+                                   c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p],
     },
     "attention_general_tc": {
         "akas_attention_general_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
                                       c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int,
-                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p],
         "akas_attention_general_tc_takes": [c_int, c_int],
     },
     "conv": {
@@ -195,6 +207,8 @@ _PART_FILES = {
     "short_conv": lambda dtype: ["conv"],
     "attention_general": lambda dtype: ["attention_general"] + (["attention_general_tc"] if dtype == torch.bfloat16 else []),
     "recurrent": lambda dtype: ["recurrent"],
+    "moe": lambda dtype: ["moe"],
+    "rope": lambda dtype: ["rope"],
 }
 
 
@@ -1227,14 +1241,37 @@ def delta_scan(q, k, v, beta, g, state, cu_seqlens, slots, heads, kv_heads, dim,
 
 
 @_flushes
-def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype):
+def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype, gate_activation="silu", out=None, out_scale=1.0):
     n = o.shape[0]
     if o.dtype != torch.float32 or not o.is_contiguous() or o.shape[1] != heads * vdim:
         raise ValueError("gated_rmsnorm takes dense float32 o [N, heads * vdim]")
+    if gate_activation not in ("silu", "sigmoid"):
+        raise ValueError(f"unknown gate activation {gate_activation!r}")
     gp, ldg = _rows(gate, "gate")
-    out = torch.empty((n, heads * vdim), dtype=out_dtype, device=o.device)
-    _check(_fn("recurrent", "akas_gated_rmsnorm")(_ptr(o), _ptr(weight), float(eps), gp, ldg, _ptr(out), n, heads, vdim,
-                                                 _code(gate), _CODE[out_dtype], _stream()), "gated_rmsnorm")
+    if out is None:
+        out = torch.empty((n, heads * vdim), dtype=out_dtype, device=o.device)
+    elif out.shape != (n, heads * vdim):
+        raise ValueError("gated_rmsnorm: out must be [N, heads * vdim]")
+    op, ldo = _rows(out, "out")
+    _check(_fn("recurrent", "akas_gated_rmsnorm")(_ptr(o), _ptr(weight), float(eps), gp, ldg, op, n, heads, vdim,
+                                                 _code(gate), _code(out), int(gate_activation == "sigmoid"),
+                                                 float(out_scale), ldo, _stream()), "gated_rmsnorm")
+    return out
+
+
+@_flushes
+def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_scale, activation=None, write=True):
+    n = q.shape[0]
+    if q.dtype != k.dtype or q.dtype != v.dtype or decay.dtype != torch.float32 or decay.numel() != heads:
+        raise ValueError("decay_scan takes q, k, v of one dtype and a float32 decay per head")
+    if activation not in (None, "silu"):
+        raise ValueError(f"unknown activation {activation!r}")
+    (qp, ldq), (kp, ldk), (vp, ldv) = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
+    sp, stride = _slot_rows(state, "state")
+    out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
+    _check(_fn("recurrent", "akas_decay_scan")(qp, ldq, kp, ldk, vp, ldv, _ptr(decay), sp, stride, _ptr(cu_seqlens), _ptr(slots),
+                                              _ptr(out), n, slots.numel(), heads, dim, vdim, float(q_scale),
+                                              int(activation == "silu"), int(bool(write)), _code(q), _stream()), "decay_scan")
     return out
 
 
@@ -1243,16 +1280,22 @@ def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype):
 
 @_flushes
 def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, k_pool, v_pool, block_table,
-                  seq_of_token, positions, page_size, write=True):
+                  seq_of_token, positions, page_size, write=True, cos=None, sin=None, interleaved=False):
     n = q.shape[0]
     if not (q.dtype == k.dtype == v.dtype == k_pool.dtype == v_pool.dtype):
         raise TypeError("qk_norm_store: q, k, v and the pages must have one dtype")
+    rot = 0
+    if cos is not None:
+        rot = 2 * cos.shape[1]
+        if cos.dtype != torch.float32 or sin.shape != cos.shape or cos.shape[0] != n or rot > dim:
+            raise ValueError("qk_norm_store: rotary tables must be float32 [N, rot / 2] with rot <= dim")
+        _dense(cos, "cos"), _dense(sin, "sin")
     (qp, ldq), (kp, ldk), (vp, ldv) = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
     out = torch.empty((n, heads * dim), dtype=q.dtype, device=q.device)
     _check(_fn("attention_general", "akas_qk_norm_store")(
         qp, ldq, kp, ldk, vp, ldv, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(out), _ptr(k_pool), _ptr(v_pool),
         _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions), page_size, n, heads, kv_heads, dim, vdim,
-        int(bool(write)), _code(q), _stream()), "qk_norm_store")
+        int(bool(write)), _code(q), _ptr(cos), _ptr(sin), rot, int(bool(interleaved)), _stream()), "qk_norm_store")
     return out
 
 
@@ -1266,21 +1309,28 @@ if general_attention not in ("mma", "plain"):
 
 @_flushes
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
-                      r1, r2, sink, gate, page_size, ctx=None):
+                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0):
     n = q.shape[0]
     kh, d, vd = k_pool.shape[1], k_pool.shape[3], v_pool.shape[3]
     heads = q.shape[1] // d
     _dense(q, "q")
     if q.dtype != k_pool.dtype or (gate is not None and gate.dtype != q.dtype):
         raise TypeError("attention_general: q, the pages and the gate must have one dtype")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != heads):
+        raise ValueError("attention_general: sinks must be float32 [heads]")
     gp, ldg = _rows(gate, "gate") if gate is not None else (None, 0)
-    out = torch.empty((n, heads * vd), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((n, heads * vd), dtype=q.dtype, device=q.device)
+    elif out.shape != (n, heads * vd) or out.dtype != q.dtype:
+        raise ValueError("attention_general: out must be [N, heads * value_dim] in q's dtype")
+    op, ldo = _rows(out, "out")
+    tail = (_ptr(sinks), float(out_scale), ldo)
     options = (float(scale), int(window or 0), int(keep_first or 0), float(softcap or 0.0), _ptr(r1), _ptr(r2),
                int(bool(sink)), gp, ldg, page_size)
     singles = n  # tokens at the front that are left to the kernel for any sizes
     lens = getattr(ctx, "query_lens", ()) if ctx is not None else ()
     if (general_attention == "mma" and q.dtype == torch.bfloat16 and lens
-            and _fn("attention_general_tc", "akas_attention_general_tc_takes")(d, vd)):
+            and ldo % 2 == 0 and op % 4 == 0 and _fn("attention_general_tc", "akas_attention_general_tc_takes")(d, vd)):
         # The single tokens at the step's front (decoding requests) as one launch whose blocks hold the query heads of
         # a key/value head; then the requests from the first that brings more, as 64-query tiles. The kernel finds its
         # tiles from cu_seqlens and addresses block tables by request: both start at the launch's first request.
@@ -1293,15 +1343,75 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
             for start, requests, tiles, packed in launches:
                 err = _fn("attention_general_tc", "akas_attention_general_tc")(
                     _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table[start:]), block_table.shape[1],
-                    _ptr(ctx.cu_seqlens[start:]), _ptr(positions), _ptr(out), *options, tiles, heads, kh, d, vd, requests,
-                    packed, _stream())
+                    _ptr(ctx.cu_seqlens[start:]), _ptr(positions), op, *options, tiles, heads, kh, d, vd, requests,
+                    packed, *tail, _stream())
                 _check(err, "attention_general (tensor cores)")
             singles = 0
     if singles:
         _check(_fn("attention_general", "akas_attention_general")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions),
-            _ptr(out), *options, singles, heads, kh, d, vd, _code(q), _stream()), "attention_general")
+            op, *options, singles, heads, kh, d, vd, _code(q), *tail, _stream()), "attention_general")
     return out
+
+
+# --------------------------------------------------------------------------- routed experts, parallel blocks
+
+
+@_flushes
+def moe_route(h, w_router, correction, groups, keep, top):
+    n, c = h.shape
+    r = w_router.shape[0]
+    if w_router.dtype != torch.float32 or correction.dtype != torch.float32 or w_router.shape[1] != c or correction.numel() != r:
+        raise ValueError("moe_route takes a float32 router matrix [R, C] and correction [R]")
+    hp, ldh = _rows(h, "h")
+    chosen = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    _check(_fn("moe", "akas_moe_route")(hp, ldh, _ptr(_dense(w_router, "w_router")), _ptr(correction), _ptr(chosen),
+                                       _ptr(weights), n, c, r, int(groups), int(keep), int(top), _code(h), _stream()),
+           "moe_route")
+    return chosen, weights
+
+
+@_flushes
+def moe_experts(h, w_gate_up, w_down, chosen, weights):
+    n, c = h.shape
+    experts, f2, _ = w_gate_up.shape
+    f, top = f2 // 2, chosen.shape[1]
+    if w_gate_up.dtype != h.dtype or w_down.dtype != h.dtype or w_down.shape != (experts, c, f) or w_gate_up.shape[2] != c:
+        raise ValueError("moe_experts takes h [N, C], w_gate_up [E, 2 F, C] and w_down [E, C, F] of one dtype")
+    hp, ldh = _rows(h, "h")
+    act = torch.empty((n * top, f), dtype=h.dtype, device=h.device)
+    out = torch.empty((n, c), dtype=torch.float32, device=h.device)
+    _check(_fn("moe", "akas_moe_gate_up")(hp, ldh, _ptr(_dense(w_gate_up, "w_gate_up")), _ptr(chosen), _ptr(act), n, top, c, f,
+                                         experts, _code(h), _stream()), "moe_gate_up")
+    _check(_fn("moe", "akas_moe_down")(hp, ldh, _ptr(_dense(w_down, "w_down")), _ptr(chosen), _ptr(weights), _ptr(act),
+                                      _ptr(out), n, top, c, f, experts, _code(h), _stream()), "moe_down")
+    return out
+
+
+_ones = {}
+
+
+def _ones_like_row(c: int, device):
+    t = _ones.get((c, device))
+    if t is None:
+        t = _ones[(c, device)] = torch.ones(c, dtype=torch.float32, device=device)
+    return t
+
+
+@_flushes
+def scaled_add(x, a, scale_a, b, scale_b, mult):
+    """x += mult * (scale_a * a + scale_b * b) in place on float32 x [N, C]; scales float32 [C] (None: ones); b may be None."""
+    n, c = x.shape
+    for t in (x, a) + ((b,) if b is not None else ()):
+        if t.dtype != torch.float32 or t.shape != (n, c) or not t.is_contiguous():
+            raise ValueError("scaled_add takes dense float32 tensors [N, C]")
+    scale_a = _ones_like_row(c, x.device) if scale_a is None else scale_a
+    if b is not None and scale_b is None:
+        scale_b = _ones_like_row(c, x.device)
+    _check(_fn("elementwise", "akas_scaled_add")(_ptr(x), _ptr(a), _ptr(scale_a), _ptr(b), _ptr(scale_b) if b is not None else None,
+                                                float(mult), n, c, _stream()), "scaled_add")
+    return x
 
 
 # --------------------------------------------------------------------------- sampling

@@ -300,6 +300,29 @@ def gla_scan(q, k, v, alpha, state, cu_seqlens, slots, heads, dim, vdim, q_scale
     return o.reshape(n, heads * vdim)
 
 
+def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_scale, activation=None, write=True):
+    """Per request and head, token by token: S <- decay_h S + k_t v_t^T; o_t = S^T (q_scale q_t) with one constant
+    decay per head (float32 [heads]); ``activation="silu"``: q, k and v pass silu first.
+    q, k [N, heads * dim], v [N, heads * vdim] -> o float32 [N, heads * vdim]; state [slots, heads, vdim, dim]."""
+    n = q.shape[0]
+    o = torch.zeros((n, heads, vdim), dtype=torch.float32, device=q.device)
+    qf, kf, vf = (t.to(torch.float64) for t in (q, k, v))
+    if activation == "silu":
+        qf, kf, vf = (t * torch.sigmoid(t) for t in (qf, kf, vf))
+    qf = qf.reshape(n, heads, dim) * q_scale
+    kf = kf.reshape(n, heads, dim)
+    vf = vf.reshape(n, heads, vdim)
+    df = decay.to(torch.float64).reshape(heads, 1, 1)
+    for slot, a, b in _requests(cu_seqlens, slots):
+        s = state[slot].to(torch.float64)
+        for t in range(a, b):
+            s = df * s + vf[t][:, :, None] * kf[t][:, None, :]
+            o[t] = torch.einsum("hvd,hd->hv", s, qf[t]).to(torch.float32)
+        if write:
+            state[slot] = s.to(torch.float32)
+    return o.reshape(n, heads * vdim)
+
+
 def causal_conv_silu(x, taps, state, cu_seqlens, seq_of_token, slots, write=True):
     """silu of a causal depthwise convolution over each request's tokens: y_t = silu(sum_j taps[:, j] x_(t - L + 1 + j)),
     inputs before the step's first token from ``state`` (zero at a request's start). x [N, C] -> float32 [N, C]."""
@@ -354,30 +377,55 @@ def delta_scan(q, k, v, beta, g, state, cu_seqlens, slots, heads, kv_heads, dim,
     return o.reshape(n, heads * vdim)
 
 
-def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype):
+def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype, gate_activation="silu", out=None, out_scale=1.0):
     """Each head of o [N, heads * vdim] over its root mean square (eps under the root), times weight [vdim], times
-    silu(gate) [N, heads * vdim]."""
+    silu(gate) [N, heads * vdim] (or, ``gate_activation="sigmoid"``, sigmoid(gate)), times ``out_scale``; written into
+    ``out`` (a view [N, heads * vdim] whose rows may be parts of wider rows) where that is given. A norm over all
+    heads together is the call with heads = 1."""
     n = o.shape[0]
     of = o.to(torch.float64).reshape(n, heads, vdim)
     of = of / torch.sqrt((of * of).mean(dim=-1, keepdim=True) + eps) * weight.to(torch.float64)
     gf = gate.to(torch.float64)
-    return (of.reshape(n, heads * vdim) * gf * torch.sigmoid(gf)).to(out_dtype)
+    act = torch.sigmoid(gf) if gate_activation == "sigmoid" else gf * torch.sigmoid(gf)
+    y = of.reshape(n, heads * vdim) * act * out_scale
+    if out is not None:
+        out.copy_(y.to(out.dtype))
+        return out
+    return y.to(out_dtype)
 
 
 # --------------------------------------------------------------------------- general attention
 
 
 def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, k_pool, v_pool, block_table,
-                  seq_of_token, positions, page_size, write=True):
-    """Per-head RMSNorm (plain weight; None: no norm) of q [N, heads * dim] and k [N, kv_heads * dim]; the normed k
-    and v [N, kv_heads * vdim] go into the pages (k pages [.., kv_heads, page, dim], v pages [.., kv_heads, page,
-    vdim]); returns the normed q, contiguous, in the pools' dtype."""
+                  seq_of_token, positions, page_size, write=True, cos=None, sin=None, interleaved=False):
+    """Per-head RMSNorm (plain weight; None: no norm) of q [N, heads * dim] and k [N, kv_heads * dim], then, where
+    ``cos`` and ``sin`` (float32 [N, rot / 2]) are given, the rotation of the first ``rot`` channels of every head of
+    q and k: channel 2i with 2i + 1 (``interleaved``) or i with i + rot / 2. k and the untouched v [N, kv_heads * vdim]
+    go into the pages (k pages [.., kv_heads, page, dim], v pages [.., kv_heads, page, vdim]); returns q, contiguous,
+    in the pools' dtype."""
     n = q.shape[0]
     qf = q.to(torch.float32).reshape(n, heads, dim)
     kf = k.to(torch.float32).reshape(n, kv_heads, dim)
     if q_weight is not None:
         qf = rmsnorm(qf, q_weight, eps, False, torch.float32)
         kf = rmsnorm(kf, k_weight, eps, False, torch.float32)
+    if cos is not None:
+        half = cos.shape[1]
+        c, sn = cos[:, None, :].to(torch.float32), sin[:, None, :].to(torch.float32)
+
+        def turn(x):
+            x = x.clone()
+            a = x[..., 0 : 2 * half : 2] if interleaved else x[..., :half]
+            b = x[..., 1 : 2 * half : 2] if interleaved else x[..., half : 2 * half]
+            ra, rb = a * c - b * sn, b * c + a * sn
+            if interleaved:
+                x[..., 0 : 2 * half : 2], x[..., 1 : 2 * half : 2] = ra, rb
+            else:
+                x[..., :half], x[..., half : 2 * half] = ra, rb
+            return x
+
+        qf, kf = turn(qf), turn(kf)
     if write:
         live, page, off = _page_addresses(block_table, seq_of_token, positions, page_size)
         k_pool[page[live], :, off[live]] = kf[live].to(k_pool.dtype)
@@ -386,16 +434,18 @@ def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, 
 
 
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
-                      r1, r2, sink, gate, page_size, ctx=None):
+                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0):
     """Attention of every token over the keys of its request that it sees: j <= i and (no window, or i - j < window,
     or j < keep_first). score = q . k * scale; with softcap, cap * tanh(score / cap); with r1 and r2 (float32
     [heads]), minus r1_h * ln(1 + r2_h * (i - j)); softmax over the keys, with ``sink`` one more term exp(0) in the
-    denominator; the head's output times sigmoid(gate[n, h]) where ``gate`` [N, heads] is given.
-    q [N, heads * dim] -> [N, heads * vdim] in q's dtype."""
+    denominator, or with ``sinks`` (float32 [heads]) the term exp(sinks_h); the head's output times
+    sigmoid(gate[n, h]) where ``gate`` [N, heads] is given, times ``out_scale``.
+    q [N, heads * dim] -> [N, heads * vdim] in q's dtype, written into ``out`` (rows may be parts of wider rows) where given."""
     n = q.shape[0]
     kh, d, vd = k_pool.shape[1], k_pool.shape[3], v_pool.shape[3]
     heads = q.shape[1] // d
     group = heads // kh
+    given = out
     out = torch.zeros((n, heads, vd), dtype=torch.float64, device=q.device)
     seqs, poss = seq_of_token.tolist(), positions.tolist()
     for t in range(n):
@@ -417,11 +467,76 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
             dist = (p - idx).to(torch.float64)
             s = s - r1.to(torch.float64).reshape(kh, group, 1) * torch.log1p(r2.to(torch.float64).reshape(kh, group, 1) * dist)
         top = s.max(dim=-1, keepdim=True).values
-        if sink:
-            top = top.clamp(min=0.0)
+        level = None
+        if sinks is not None:
+            level = sinks.to(torch.float64).reshape(kh, group, 1)
+        elif sink:
+            level = torch.zeros((kh, group, 1), dtype=torch.float64, device=q.device)
+        if level is not None:
+            top = torch.maximum(top, level)
         e = torch.exp(s - top)
-        denom = e.sum(dim=-1, keepdim=True) + (torch.exp(-top) if sink else 0.0)
+        denom = e.sum(dim=-1, keepdim=True) + (torch.exp(level - top) if level is not None else 0.0)
         out[t] = torch.einsum("kgs,skd->kgd", e / denom, vals).reshape(heads, vd)
     if gate is not None:
         out = out * torch.sigmoid(gate.to(torch.float64))[:, :, None]
-    return out.reshape(n, heads * vd).to(q.dtype)
+    result = (out * out_scale).reshape(n, heads * vd)
+    if given is not None:
+        given.copy_(result.to(given.dtype))
+        return given
+    return result.to(q.dtype)
+
+
+# --------------------------------------------------------------------------- routed experts, parallel blocks
+
+
+def moe_route(h, w_router, correction, groups, keep, top):
+    """For every row of h [N, C]: scores = softmax(h . w_router^T) over the R router outputs (float32 w_router
+    [R, C]); choice scores = scores + correction [R]; the outputs form ``groups`` equal groups of neighbours whose
+    score is their largest choice score, and only outputs of the ``keep`` best groups can be chosen; the ``top``
+    largest choice scores win (ties: the lower index). Returns (chosen int32 [N, top], weights float32 [N, top]): the
+    chosen outputs in the order of their choice scores and their plain scores over their sum (+ 1e-20)."""
+    n = h.shape[0]
+    r = w_router.shape[0]
+    s = torch.softmax(h.to(torch.float32) @ w_router.to(torch.float32).T, dim=-1)
+    pick = s + correction.to(torch.float32)
+    if groups > 1 and keep < groups:
+        best = pick.reshape(n, groups, r // groups).max(dim=-1).values
+        order = torch.argsort(best, dim=-1, descending=True, stable=True)
+        stays = torch.zeros((n, groups), dtype=torch.bool, device=h.device)
+        stays.scatter_(1, order[:, :keep], True)
+        pick = pick.masked_fill(~stays.repeat_interleave(r // groups, dim=1), float("-inf"))
+    chosen = torch.argsort(pick, dim=-1, descending=True, stable=True)[:, :top]
+    w = torch.gather(s, 1, chosen)
+    w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
+    return chosen.to(torch.int32), w
+
+
+def moe_experts(h, w_gate_up, w_down, chosen, weights):
+    """out[n] = sum_k weights[n, k] * expert_(chosen[n, k])(h[n]) in float32 [N, C]. Expert e < E computes
+    w_down[e] (silu(gate) * up) with [gate; up] = w_gate_up[e] h (w_gate_up [E, 2 F, C], w_down [E, C, F]; the hidden
+    activations are rounded to h's dtype, as the kernels round them); an expert number from E on returns h itself."""
+    n, c = h.shape
+    e_count, f2, _ = w_gate_up.shape
+    out = torch.zeros((n, c), dtype=torch.float32, device=h.device)
+    hf = h.to(torch.float32)
+    for k in range(chosen.shape[1]):
+        for e in torch.unique(chosen[:, k]).tolist():
+            rows = (chosen[:, k] == e).nonzero().flatten()
+            g = weights[rows, k][:, None]
+            if e >= e_count:
+                out[rows] += g * hf[rows]
+                continue
+            gu = hf[rows] @ w_gate_up[e].to(torch.float32).T
+            act = (torch.nn.functional.silu(gu[:, : f2 // 2]) * gu[:, f2 // 2 :]).to(h.dtype).to(torch.float32)
+            out[rows] += g * (act @ w_down[e].to(torch.float32).T)
+    return out
+
+
+def scaled_add(x, a, scale_a, b, scale_b, mult):
+    """x += mult * (scale_a * a + scale_b * b) in place on float32 x [N, C]; the scales are float32 [C] (None: ones),
+    b may be None."""
+    total = a if scale_a is None else a * scale_a
+    if b is not None:
+        total = total + (b if scale_b is None else b * scale_b)
+    x += mult * total
+    return x

@@ -20,15 +20,17 @@ from .base import (
 )
 from .attention import Attention
 from .block import ARRANGEMENTS, Block
+from .moe import RoutedExperts
 from .norm import RMSNorm
+from .parallel import ParallelMixer
 from .polynorm import PolyNormMLP
-from .recurrent import GatedDelta, GatedLinearAttention
+from .recurrent import DecayedLinearAttention, GatedDelta, GatedLinearAttention
 from .rope import Rope
 from .shortconv import ShortConv
 from .swiglu import SwiGLU
 
 __all__ = [
-    "ARRANGEMENTS", "Attention", "Block", "FeedForward", "GatedDelta", "GatedLinearAttention", "Mixer", "PolyNormMLP", "Normed", "PagedKVSpec", "PagedSpec", "Param", "Part", "RMSNorm",
+    "ARRANGEMENTS", "Attention", "Block", "DecayedLinearAttention", "ParallelMixer", "RoutedExperts", "FeedForward", "GatedDelta", "GatedLinearAttention", "Mixer", "PolyNormMLP", "Normed", "PagedKVSpec", "PagedSpec", "Param", "Part", "RMSNorm",
     "Rope", "Runtime", "ShortConv", "StateSpec", "SwiGLU", "build_part", "project", "project_swiglu", "register_ffn", "register_mixer",
     "register_norm", "register_position",
 ]

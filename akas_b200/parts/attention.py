@@ -9,10 +9,12 @@ read from the pages, so a portion of a prompt attends to what earlier steps left
 and to itself; the output product, added to the residual.
 
 A layer whose spec asks for more than that (value heads of another size than the keys', a capped score, a
-logarithmic distance penalty, first tokens kept behind the window, a sink in the softmax's denominator, a gate
-per head on the output) runs the same steps on the general kernels: one product for q, k, v and the gate's
-logits, QK-norm and page write (``ops.qk_norm_store``), attention with the options as arguments
-(``ops.attention_general``), the output product.
+logarithmic distance penalty, first tokens kept behind the window, a sink in the softmax's denominator (exp(0) or a
+learned logit per head), a gate per head on the output, values that are the keys as projected, rotary pairs of
+neighbouring channels) runs the same steps on the general kernels: one product for q, k, v and the gate's
+logits, QK-norm, rotation and page write (``ops.qk_norm_store``), attention with the options as arguments
+(``ops.attention_general``), the output product. ``core`` is that sequence without the two products, for a mixer
+that stacks this one's matrices with its neighbours' (``parts/parallel.py``).
 """
 
 from __future__ import annotations
@@ -29,7 +31,9 @@ class Attention(Mixer):
 
     @classmethod
     def kernels(cls, spec):
-        return ("attention_general",) if getattr(spec, "general", False) else ("attention",)
+        if not getattr(spec, "general", False):
+            return ("attention",)
+        return ("attention_general", "rope") if spec.position is not None else ("attention_general",)
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -39,8 +43,10 @@ class Attention(Mixer):
         self.general = bool(getattr(s, "general", False))
         if not self.general and (s.head_dim % 16 or s.head_dim > 256):
             raise ValueError(f"head_dim {s.head_dim} must be a multiple of 16, at most 256")
-        if self.general and s.position is not None:
-            raise ValueError("the general attention kernels take no position encoding of q and k")
+        if s.sink not in (False, True, "learned"):
+            raise ValueError(f"unknown sink {s.sink!r}; known: False, True, 'learned'")
+        if getattr(s, "values_are_keys", False) and s.value_dim != s.head_dim:
+            raise ValueError(f"values that are the keys have the keys' size: {s.value_dim} is not {s.head_dim}")
         if self.general and getattr(s, "gate", None) not in (None, "head"):
             raise ValueError(f"unknown output gate {s.gate!r}; known: 'head'")
         if self.general and s.keep_first and not s.window:
@@ -49,9 +55,11 @@ class Attention(Mixer):
         self.k_norm = build_part("norm", s.qk_norm, runtime)
         self.position = build_part("position", s.position, runtime)
         self.scale = s.scale if s.scale is not None else s.head_dim ** -0.5
+        if self.general and self.position is not None and not hasattr(self.position, "tables"):
+            raise ValueError("the general attention kernels take a position encoding by rotary tables only")
         self.w_qkv = None
         self.w_out = None
-        self.r1 = self.r2 = None
+        self.r1 = self.r2 = self.sinks = None
 
     def _n(self, local):
         return renamed(self.spec, local)
@@ -65,6 +73,10 @@ class Attention(Mixer):
             self._n("v_proj.weight"): Param((s.num_kv_heads * vd, s.hidden_size)),
             self._n("out_proj.weight"): Param((s.hidden_size, s.num_heads * vd)),
         }
+        if self.general and s.values_are_keys:
+            del p[self._n("v_proj.weight")]
+        if self.general and s.sink == "learned":
+            p[self._n("sink")] = Param((s.num_heads,), role="vector")
         if self.general and s.gate == "head":
             p[self._n("gate.weight")] = Param((s.num_heads, s.hidden_size))
         if self.general and s.distance_bias:
@@ -78,10 +90,14 @@ class Attention(Mixer):
 
     def load(self, get):
         if self.general:
-            parts = [get(self._n("q_proj.weight")), get(self._n("k_proj.weight")), get(self._n("v_proj.weight"))]
+            parts = [get(self._n("q_proj.weight")), get(self._n("k_proj.weight"))]
+            if not self.spec.values_are_keys:
+                parts.append(get(self._n("v_proj.weight")))
             if self.spec.gate == "head":
                 parts.append(get(self._n("gate.weight")))
             self.w_qkv = stack_rows(parts)
+            if self.spec.sink == "learned":
+                self.sinks = get(self._n("sink"))
             if self.spec.distance_bias:
                 self.r1, self.r2 = get(self._n("r1")), get(self._n("r2"))
         else:
@@ -100,25 +116,50 @@ class Attention(Mixer):
                                v_head_dim=s.value_dim)
         return PagedKVSpec(s.num_kv_heads, s.head_dim, s.window)
 
-    def _forward_general(self, x, ctx, cache, residual, write):
+    @property
+    def w_in(self):
+        """The stacked input matrices (general layers): what ``core`` wants the product of."""
+        return self.w_qkv
+
+    def core(self, proj, ctx, cache, write=True, out=None, out_scale=1.0):
+        """Everything between the input product ``proj`` [N, rows of w_in] and the output product: the heads'
+        outputs [N, heads * value_dim] times ``out_scale``, written to ``out`` where that is given (a view whose rows
+        may be part of wider rows)."""
+        if not self.general:
+            raise ValueError("core() is the general layers' sequence")
         s, ops = self.spec, self.rt.ops
-        proj = project(self.rt, x, self.w_qkv)
-        nq, nk, nv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.value_dim
-        q, k, v = proj[:, :nq], proj[:, nq : nq + nk], proj[:, nq + nk : nq + nk + nv]
+        nq, nk = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
+        nv = 0 if s.values_are_keys else s.num_kv_heads * s.value_dim
+        q, k = proj[:, :nq], proj[:, nq : nq + nk]
+        v = k if s.values_are_keys else proj[:, nq + nk : nq + nk + nv]
         gate = proj[:, nq + nk + nv : nq + nk + nv + s.num_heads] if s.gate == "head" else None
         norm = self.q_norm.spec if self.q_norm is not None else None
         if norm is not None and norm.zero_centered:
             raise ValueError("the general attention kernels take a plain QK-norm weight")
         table = ctx.block_table(cache.group)
+        rotary = {}
+        if self.position is not None:
+            cos, sin = self.position.tables(ctx)
+            rotary = dict(cos=cos, sin=sin, interleaved=self.position.interleaved)
         qn = ops.qk_norm_store(
             q, k, v, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
             self.q_norm.weight if norm else None, self.k_norm.weight if norm else None, norm.eps if norm else 0.0,
-            cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, cache.page_size, write=write,
+            cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, cache.page_size, write=write, **rotary,
         )
-        out = ops.attention_general(
+        more = {}
+        if self.sinks is not None:
+            more["sinks"] = self.sinks
+        if out is not None:
+            more["out"] = out
+        if out_scale != 1.0:
+            more["out_scale"] = out_scale
+        return ops.attention_general(
             qn, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, self.scale, s.window, s.keep_first,
-            s.softcap, self.r1, self.r2, s.sink, gate, cache.page_size, ctx,
+            s.softcap, self.r1, self.r2, s.sink is True, gate, cache.page_size, ctx, **more,
         )
+
+    def _forward_general(self, x, ctx, cache, residual, write):
+        out = self.core(project(self.rt, x, self.w_qkv), ctx, cache, write)
         return project(self.rt, out, self.w_out, residual=residual)
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):

@@ -232,6 +232,14 @@ def mixer_class(spec) -> type:
     return _REGISTRIES["mixer"][kind]
 
 
+def ffn_class(spec) -> type:
+    """The class registered for a feed-forward spec's kind."""
+    kind = getattr(spec, "kind", None)
+    if kind not in _REGISTRIES["ffn"]:
+        raise KeyError(f"no ffn registered for kind {kind!r}; registered: {sorted(_REGISTRIES['ffn'])}")
+    return _REGISTRIES["ffn"][kind]
+
+
 def build_part(family: str, spec, runtime: Runtime):
     """The part that ``spec.kind`` names in the registry of ``family``; ``None`` for a ``None`` spec."""
     if spec is None:

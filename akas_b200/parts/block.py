@@ -1,11 +1,15 @@
 """A block: a mixer and (unless the layer has none) a feed-forward, each behind its norm, around a float32 residual stream.
 
 ``pre_norm`` (the only arrangement LFM2 uses, src/akas/models/lfm2/_composition.py:189,308-309,356
-in kreasof-ai/akas): h += mixer(norm(h)); h += ffn(norm(h)). Other arrangements are
+in kreasof-ai/akas): h += mixer(norm(h)); h += ffn(norm(h)). ``parallel``: one norm n = norm(h) that the mixer and
+the feed-forward both read, h += m * (s1 * mixer(n) + s2 * ffn(n)) with a constant m and a learned scale per channel
+for each sublayer (the two results are float32 and meet the residual stream in one kernel). Other arrangements are
 added to ``ARRANGEMENTS`` as functions of (block, h, ctx, cache, write).
 """
 
 from __future__ import annotations
+
+import torch
 
 from .base import Param, Runtime, build_part
 
@@ -24,7 +28,21 @@ def _pre_norm(block, h, ctx, cache, write):
     return block.ffn.forward(_normed(block.ffn_norm, block.ffn, h), ctx, residual=h)
 
 
-ARRANGEMENTS = {"pre_norm": _pre_norm}
+def _float32_result(part, *args, **kwargs):
+    """A sublayer's result without a residual, in float32: asked of the part where it can say so, else widened."""
+    if getattr(part, "takes_out_dtype", False):
+        return part.forward(*args, out_dtype=torch.float32, **kwargs)
+    return part.forward(*args, **kwargs).to(torch.float32)
+
+
+def _parallel(block, h, ctx, cache, write):
+    n = block.mixer_norm.forward(h)
+    a = _float32_result(block.mixer, n, ctx, cache, residual=None, write=write)
+    b = None if block.ffn is None else _float32_result(block.ffn, n, ctx, residual=None)
+    return block.mixer.rt.ops.scaled_add(h, a, block.mixer_scale, b, block.ffn_scale, block.spec.residual_multiplier)
+
+
+ARRANGEMENTS = {"pre_norm": _pre_norm, "parallel": _parallel}
 
 
 class Block:
@@ -37,6 +55,7 @@ class Block:
         self.mixer_norm = build_part("norm", spec.mixer_norm, runtime)
         self.ffn_norm = build_part("norm", spec.ffn_norm, runtime)
         self._run = ARRANGEMENTS[spec.arrangement]
+        self.mixer_scale = self.ffn_scale = None  # the parallel arrangement's scales per channel, where the layer names them
         # Whether every part of the block reaches its tensors through the runtime's operations only (see Part.chain_safe)
         self.chain_safe = all(getattr(part, "chain_safe", False)
                               for part in (self.mixer, self.ffn, self.mixer_norm, self.ffn_norm) if part is not None)
@@ -49,9 +68,16 @@ class Block:
             out.update({s.ffn_prefix + k: v for k, v in self.ffn.params().items()})
         (norm_param,) = self.mixer_norm.params().values()
         out[s.mixer_norm_name] = norm_param
-        if self.ffn is not None:
+        width = norm_param.shape
+        if s.mixer_scale_name is not None:
+            out[s.mixer_scale_name] = Param(width, role="vector", mean=1.0)
+        if s.ffn_scale_name is not None and self.ffn is not None:
+            out[s.ffn_scale_name] = Param(width, role="vector", mean=1.0)
+        if self.ffn is not None and self.ffn_norm is not None:
             (norm_param,) = self.ffn_norm.params().values()
             out[s.ffn_norm_name] = norm_param
+        elif self.ffn is not None:
+            pass  # an arrangement in which the feed-forward reads the mixer's norm
         elif s.ffn_norm_name is not None:
             # a layer without a feed-forward: a checkpoint may still carry the norm that would precede one
             out[s.ffn_norm_name] = Param(norm_param.shape, role="vector", optional=True, mean=norm_param.mean)
@@ -63,7 +89,12 @@ class Block:
         self.mixer_norm.load(lambda _name: get(s.mixer_norm_name))
         if self.ffn is not None:
             self.ffn.load(lambda name: get(s.ffn_prefix + name))
-            self.ffn_norm.load(lambda _name: get(s.ffn_norm_name))
+            if self.ffn_norm is not None:
+                self.ffn_norm.load(lambda _name: get(s.ffn_norm_name))
+        if s.mixer_scale_name is not None:
+            self.mixer_scale = get(s.mixer_scale_name)
+        if s.ffn_scale_name is not None and self.ffn is not None:
+            self.ffn_scale = get(s.ffn_scale_name)
 
     def forward(self, h, ctx, cache=None, write=True):
         return self._run(self, h, ctx, cache, write)

@@ -1,12 +1,16 @@
-"""Mixers whose cache is a matrix state per head: gated linear attention and the gated delta rule.
+"""Mixers whose cache is a matrix state per head: gated linear attention, linear attention with a constant decay per
+head, and the gated delta rule.
 
-Both keep, per request and head, a float32 matrix S [key_dim, value_dim] in the request's state slot, update it
+All keep, per request and head, a float32 matrix S [key_dim, value_dim] in the request's state slot, update it
 token by token and read it out with the token's query, so a step of any length continues from what earlier
 steps left and a request's cost per token does not grow with its length.
 
 * ``GatedLinearAttention``: S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T q_t, with a decay per key channel
   alpha = sigmoid(W_a2 (W_a1 x) + b)^(1 / tau). (Yang et al., "Gated Linear Attention Transformers with
   Hardware-Efficient Training", state the recurrence.)
+* ``DecayedLinearAttention``: S <- decay_h S + k_t v_t^T, o_t = S^T q_t with one constant decay per head (the
+  recurrence of Qin et al.'s "Lightning Attention-2" without its chunking); q, k and v pass silu, the read-out of all
+  heads is normed as one row, gated by sigmoid(W_g x) and projected.
 * ``GatedDelta``: S <- g_t S; u = beta_t (v_t - S^T k_t); S <- S + k_t u^T; o_t = S^T q_t, after a short causal
   convolution and silu on q, k and v and unit-length q and k. The convolution's last inputs are part of the state.
 
@@ -83,6 +87,67 @@ class GatedLinearAttention(Mixer):
         return project(self.rt, y, self.w_out, residual=residual)
 
 
+class DecayedLinearAttention(Mixer):
+    takes_normed = True
+    chain_safe = True
+
+    @classmethod
+    def kernels(cls, spec):
+        return ("recurrent",)
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        s = spec
+        if len(s.decay) != s.num_heads:
+            raise ValueError(f"{len(s.decay)} decays for {s.num_heads} heads")
+        if s.activation not in (None, "silu") or s.gate_activation not in ("sigmoid", "silu"):
+            raise ValueError(f"unknown activation {s.activation!r} or gate activation {s.gate_activation!r}")
+        self.w_in = self.w_out = self.norm = self.decay = None
+
+    def _n(self, local):
+        return renamed(self.spec, local)
+
+    def params(self):
+        s = self.spec
+        c, hd, hv = s.hidden_size, s.num_heads * s.key_dim, s.num_heads * s.value_dim
+        return {
+            self._n("q"): Param((hd, c)),
+            self._n("k"): Param((hd, c)),
+            self._n("v"): Param((hv, c)),
+            self._n("g"): Param((hv, c)),
+            self._n("o"): Param((c, hv)),
+            self._n("norm"): Param((hv if s.whole_norm else s.value_dim,), role="vector", mean=1.0),
+        }
+
+    def load(self, get):
+        self.w_in = stack_rows([get(self._n(n)) for n in ("q", "k", "v", "g")])
+        self.norm = get(self._n("norm"))
+        self.w_out = get(self._n("o"))
+        # the decays are constants of the configuration, kept as float32 (the recurrence's own precision)
+        self.decay = torch.tensor([float(d) for d in self.spec.decay], dtype=torch.float64).to(
+            device=self.w_out.device, dtype=torch.float32)
+
+    def cache(self):
+        s = self.spec
+        return StateSpec((s.num_heads, s.value_dim, s.key_dim), torch.float32)  # S transposed, as the scan kernels keep it
+
+    def core(self, proj, ctx, cache, write=True, out=None, out_scale=1.0):
+        """From the input product ``proj`` [N, rows of w_in] to what the output product reads, times ``out_scale``."""
+        s, ops = self.spec, self.rt.ops
+        hd, hv = s.num_heads * s.key_dim, s.num_heads * s.value_dim
+        q, k, v = proj[:, :hd], proj[:, hd : 2 * hd], proj[:, 2 * hd : 2 * hd + hv]
+        gate = proj[:, 2 * hd + hv : 2 * hd + 2 * hv]
+        o = ops.decay_scan(q, k, v, self.decay, cache.state, ctx.cu_seqlens, ctx.slots, s.num_heads, s.key_dim, s.value_dim,
+                           s.q_scale, activation=s.activation, write=write)
+        heads, width = (1, hv) if s.whole_norm else (s.num_heads, s.value_dim)
+        return ops.gated_rmsnorm(o, self.norm, s.norm_eps, gate, heads, width, self.rt.dtype,
+                                 gate_activation=s.gate_activation, out=out, out_scale=out_scale)
+
+    def forward(self, x, ctx, cache=None, residual=None, write=True):
+        y = self.core(project(self.rt, x, self.w_in), ctx, cache, write)
+        return project(self.rt, y, self.w_out, residual=residual)
+
+
 class GatedDelta(Mixer):
     takes_normed = True
     chain_safe = True
@@ -156,3 +221,4 @@ class GatedDelta(Mixer):
 
 register_mixer("gated_linear_attention", GatedLinearAttention)
 register_mixer("gated_delta", GatedDelta)
+register_mixer("decayed_linear_attention", DecayedLinearAttention)

@@ -1,4 +1,4 @@
-"""Rotary position encoding, rotate-half pairing (i, i + rotary/2).
+"""Rotary position encoding, rotate-half pairing (i, i + rotary/2) or interleaved pairing (2i, 2i + 1).
 
 theta_i = position * base^(-2i/rotary). kreasof-ai/akas forms this product with a
 hi/lo split of the frequency and a two-term reduction by 2 pi so that float32 stays
@@ -25,7 +25,8 @@ class Rope(Part):
             raise ValueError(f"rotary_dim {rotary} must be even and at most head_dim {spec.head_dim}")
         i = torch.arange(rotary // 2, dtype=torch.float64)
         self.inv_freq = (torch.tensor(float(spec.theta), dtype=torch.float64) ** (-2.0 * i / rotary)).to(runtime.device)
-        self.key = ("rope", rotary, float(spec.theta))
+        self.key = ("rope", rotary, float(spec.theta))  # the tables are the same for both pairings
+        self.interleaved = bool(getattr(spec, "interleaved", False))
 
     def tables(self, ctx):
         """(cos, sin), float32 [N, rotary/2], for the tokens of this step."""
