@@ -430,7 +430,7 @@ def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, 
         live, page, off = _page_addresses(block_table, seq_of_token, positions, page_size)
         k_pool[page[live], :, off[live]] = kf[live].to(k_pool.dtype)
         v_pool[page[live], :, off[live]] = v.reshape(n, kv_heads, vdim)[live].to(v_pool.dtype)
-    return qf.reshape(n, heads * dim).to(k_pool.dtype)
+    return qf.reshape(n, heads * dim).to(k_pool.dtype).contiguous()
 
 
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,

@@ -84,9 +84,12 @@ def two_mixers(h, w, p, m, eps):
     return m["left_scale"] * left + m["right_scale"] * right
 
 
-def route(h, w, p, r):
+def route(h, w, p, r, margins=None):
     """For every token the chosen router outputs and their weights: softmax over all router outputs; the choice is
-    by score plus correction among the outputs of the best groups; the weights are the plain scores, normalised."""
+    by score plus correction among the outputs of the best groups; the weights are the plain scores, normalised.
+    ``margins``, a list, receives per token how far the choice was from going another way (the smaller of the gap
+    between the last kept and the first dropped group and the gap between the last chosen and the first unchosen
+    output): a test in reduced precision cannot hold a token whose margin is of rounding's size."""
     n = r["experts"] + r["identity"]
     s = torch.softmax(h @ w[p + "router"].T, dim=-1)
     choice = s + w[p + "correction"]
@@ -100,6 +103,13 @@ def route(h, w, p, r):
         for g in groups:
             masked[g * size : (g + 1) * size] = choice[t, g * size : (g + 1) * size]
         idx = torch.topk(masked, r["top"]).indices
+        if margins is not None:
+            ordered = torch.sort(masked, descending=True).values
+            gap = float(ordered[r["top"] - 1] - ordered[r["top"]]) if r["top"] < n else float("inf")
+            if keep < count:
+                groups_sorted = torch.sort(best, descending=True).values
+                gap = min(gap, float(groups_sorted[keep - 1] - groups_sorted[keep]))
+            margins.append(gap)
         chosen.append(idx)
         weights.append(s[t, idx] / (s[t, idx].sum() + 1e-20))
     return torch.stack(chosen), torch.stack(weights)
@@ -109,11 +119,11 @@ def expert(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def mixture(h, w, p, f):
+def mixture(h, w, p, f, margins=None):
     """The weighted sum of the chosen experts' outputs; a router output past the real experts is an expert that
     returns its input."""
     r = f["router"]
-    chosen, weights = route(h, w, p, r)
+    chosen, weights = route(h, w, p, r, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weights[t]):
@@ -121,23 +131,27 @@ def mixture(h, w, p, f):
     return out
 
 
-def layer(x, w, i, entry, cfg):
+def layer(x, w, i, entry, cfg, margins=None):
     """x + m * (ls1 * mixer(h) + ls2 * ff(h)) with ONE norm h that both sublayers read."""
     eps = cfg["norm"]["eps"]
     p = f"l{i}."
     h = rms(x, eps) * w[p + "norm1"]
     total = w[p + "ls1"] * two_mixers(h, w, p + "mix.", entry["mixer"], eps)
     if entry.get("mlp") is not None:
-        total = total + w[p + "ls2"] * mixture(h, w, p + "mlp.", entry["mlp"])
+        total = total + w[p + "ls2"] * mixture(h, w, p + "mlp.", entry["mlp"], margins)
     return x + cfg["residual_mult"] * total
 
 
-def forward(tokens, w, cfg, trace=None):
-    """Logits [T, vocab] of one sequence; ``trace``, a list, receives the residual stream after every layer."""
+def forward(tokens, w, cfg, trace=None, margins=None):
+    """Logits [T, vocab] of one sequence; ``trace``, a list, receives the residual stream after every layer, and
+    ``margins``, a list, one list per routed layer of the tokens' routing margins (see ``route``)."""
     w = {k: v.to(F) for k, v in w.items()}
     x = w["embed"][torch.as_tensor(tokens)]
     for i, entry in enumerate(cfg["layers"]):
-        x = layer(x, w, i, entry, cfg)
+        here = [] if margins is not None and entry.get("mlp") is not None else None
+        x = layer(x, w, i, entry, cfg, here)
+        if here is not None:
+            margins.append(here)
         if trace is not None:
             trace.append(x.clone())
     x = rms(x, cfg["norm"]["eps"]) * w["final.norm"]
