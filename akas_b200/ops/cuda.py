@@ -78,6 +78,15 @@ _SIGNATURES = {
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p],
         "akas_attention_general_tc_takes": [c_int, c_int],
     },
+    "moe_grouped": {
+        "akas_moe_grouped_rows": [c_int, c_int],
+        "akas_moe_grouped_takes": [c_int, c_int, c_int],
+        "akas_moe_sort": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                          c_void_p],
+        "akas_moe_grouped_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_moe_combine": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_moe_grouped_status": [],
+    },
     "conv": {
         "akas_short_conv": [c_void_p] * 8 + [c_int] * 6 + [c_void_p],
         "akas_short_conv_decode": [c_void_p] * 7 + [c_int] * 5 + [c_void_p],
@@ -207,7 +216,7 @@ _PART_FILES = {
     "short_conv": lambda dtype: ["conv"],
     "attention_general": lambda dtype: ["attention_general"] + (["attention_general_tc"] if dtype == torch.bfloat16 else []),
     "recurrent": lambda dtype: ["recurrent"],
-    "moe": lambda dtype: ["moe"],
+    "moe": lambda dtype: ["moe"] + (["moe_grouped"] if dtype == torch.bfloat16 else []),
     "rope": lambda dtype: ["rope"],
 }
 
@@ -1372,6 +1381,45 @@ def moe_route(h, w_router, correction, groups, keep, top):
     return chosen, weights
 
 
+# Which kernels run the experts in bfloat16: "auto" (default), the grouped product on the tensor cores
+# (csrc/moe_grouped.cu) for steps of more than _MOE_SIMPLE_PAIRS (token, expert) pairs and sizes it takes, the
+# token-by-token kernels (csrc/moe.cu) otherwise; "simple": those for everything.
+moe_kernels = os.environ.get("AKAS_B200_MOE", "auto")
+if moe_kernels not in ("auto", "simple"):
+    raise ValueError(f"AKAS_B200_MOE must be auto or simple, got {moe_kernels!r}")
+_MOE_SIMPLE_PAIRS = 64
+
+
+def moe_grouped_status() -> int:
+    return int(_fn("moe_grouped", "akas_moe_grouped_status")())
+
+
+def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights):
+    n, c = h.shape
+    experts, f2, _ = w_gate_up.shape
+    f, top = f2 // 2, chosen.shape[1]
+    hp, ldh = _rows(h, "h")
+    cap = int(_fn("moe_grouped", "akas_moe_grouped_rows")(n * top, experts))
+    dev = h.device
+    row_of_pair = torch.empty(n * top, dtype=torch.int32, device=dev)
+    tile_expert = torch.empty(cap // 128, dtype=torch.int32, device=dev)
+    plan = torch.empty(4, dtype=torch.int32, device=dev)
+    rows = torch.empty((cap, c), dtype=h.dtype, device=dev)
+    act = torch.empty((cap, f), dtype=h.dtype, device=dev)
+    y = torch.empty((cap, c), dtype=torch.float32, device=dev)
+    out = torch.empty((n, c), dtype=torch.float32, device=dev)
+    _check(_fn("moe_grouped", "akas_moe_sort")(hp, ldh, _ptr(chosen), _ptr(row_of_pair), _ptr(tile_expert), _ptr(plan), _ptr(rows),
+                                              n, top, c, experts, _stream()), "moe_sort", kernels=2)
+    gemm = _fn("moe_grouped", "akas_moe_grouped_gemm")
+    _check(gemm(_ptr(rows), _ptr(w_gate_up), _ptr(act), _ptr(tile_expert), _ptr(plan), cap, experts, f2, c, 2, _stream()),
+           "grouped gate and up product")
+    _check(gemm(_ptr(act), _ptr(w_down), _ptr(y), _ptr(tile_expert), _ptr(plan), cap, experts, c, f, 1, _stream()),
+           "grouped down product")
+    _check(_fn("moe_grouped", "akas_moe_combine")(hp, ldh, _ptr(y), _ptr(row_of_pair), _ptr(weights), _ptr(out), n, top, c,
+                                                 _stream()), "moe_combine")
+    return out
+
+
 @_flushes
 def moe_experts(h, w_gate_up, w_down, chosen, weights):
     n, c = h.shape
@@ -1380,6 +1428,10 @@ def moe_experts(h, w_gate_up, w_down, chosen, weights):
     if w_gate_up.dtype != h.dtype or w_down.dtype != h.dtype or w_down.shape != (experts, c, f) or w_gate_up.shape[2] != c:
         raise ValueError("moe_experts takes h [N, C], w_gate_up [E, 2 F, C] and w_down [E, C, F] of one dtype")
     hp, ldh = _rows(h, "h")
+    if (moe_kernels == "auto" and h.dtype == torch.bfloat16 and n * top > _MOE_SIMPLE_PAIRS and ldh % 8 == 0 and hp % 16 == 0
+            and _fn("moe_grouped", "akas_moe_grouped_takes")(c, f, experts)):
+        _dense(w_gate_up, "w_gate_up"), _dense(w_down, "w_down")
+        return _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights)
     act = torch.empty((n * top, f), dtype=h.dtype, device=h.device)
     out = torch.empty((n, c), dtype=torch.float32, device=h.device)
     _check(_fn("moe", "akas_moe_gate_up")(hp, ldh, _ptr(_dense(w_gate_up, "w_gate_up")), _ptr(chosen), _ptr(act), n, top, c, f,

@@ -529,8 +529,23 @@ def test_routed_experts_kernels(outputs, experts, count, keep, top, c, f, dtype)
     w_gate_up = (torch.randn(experts, 2 * f, c, generator=g) * c ** -0.5).to(dtype).cuda()
     w_down = (torch.randn(experts, c, f, generator=g) * f ** -0.5).to(dtype).cuda()
     want = reference.moe_experts(h, w_gate_up, w_down, want_c, want_w)
-    got = cuda.moe_experts(h, w_gate_up, w_down, want_c, want_w)
+    got = cuda.moe_experts(h, w_gate_up, w_down, want_c, want_w)  # 45 tokens: the grouped product in bfloat16 where it takes the sizes
     _close(got, want, 2e-5 if dtype == torch.float32 else 1e-2, "experts")
+    few = cuda.moe_experts(h[:5], w_gate_up, w_down, want_c[:5], want_w[:5])  # few pairs: token by token
+    _close(few, want[:5], 2e-5 if dtype == torch.float32 else 1e-2, "experts, few tokens")
+    if dtype == torch.bfloat16:
+        assert cuda.moe_grouped_status() == 0
+        # hundreds of tokens, so that experts get several tiles of rows and some get none; and the result of a token
+        # must not depend on what else the step holds
+        hh = torch.randn(700, c, generator=g).to(dtype).cuda()
+        cc, ww = cuda.moe_route(hh, w_router, correction, count, keep, top)
+        cc[:300] = cc[0]  # crowd one choice
+        big = cuda.moe_experts(hh, w_gate_up, w_down, cc, ww)
+        _close(big, reference.moe_experts(hh, w_gate_up, w_down, cc, ww), 1e-2, "experts, many tokens")
+        part = cuda.moe_experts(hh[100:420], w_gate_up, w_down, cc[100:420], ww[100:420])
+        if c % 8 == 0 and f % 8 == 0:
+            assert torch.equal(part, big[100:420]), "a token's experts depend on the batch"
+        assert cuda.moe_grouped_status() == 0
     # exact ties go to the lower index, and the groups' rule holds on made-up scores
     eye_h = torch.zeros(3, outputs, dtype=dtype).cuda()
     tie_c, tie_w = cuda.moe_route(eye_h, torch.eye(outputs).cuda(), torch.zeros(outputs).cuda(), count, keep, top)
