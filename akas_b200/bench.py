@@ -26,15 +26,29 @@ def synthetic_prompts(batch: int, prefix: int, vocab: int, seed: int = 17) -> Li
 
 
 def matrix_params(runner: ModelRunner) -> Dict[str, int]:
-    """Parameters of the matrix products a token passes through (per layer run, head apart)."""
+    """Parameters of the matrix products a token passes through (per layer run, head apart). Of a routed feed-forward's
+    stacked experts [experts, rows, columns] a token passes through ``top`` (less the share of identity experts)."""
     layers = 0
     for entry in runner.model.schedule:
         block = runner.model.blocks[entry.layer]
         for part in (block.mixer, block.ffn):
+            if part is None:
+                continue
             for value in vars(part).values():
                 if isinstance(value, torch.Tensor) and value.dim() == 2 and value.dtype == runner.dtype:
                     layers += value.numel()
+                elif isinstance(value, torch.Tensor) and value.dim() == 3 and value.dtype == runner.dtype:
+                    s = part.spec
+                    real = s.top * s.num_experts / (s.num_experts + s.num_identity)
+                    layers += int(value[0].numel() * real)
     return dict(layers=layers, head=runner.model.head.numel())
+
+
+def _mixer_specs(spec):
+    """The specs of the mixers a layer's mixer is made of (itself, unless it holds several side by side)."""
+    if getattr(spec, "kind", "") == "parallel_mixer":
+        return [branch for _, branch, _ in spec.branches]
+    return [spec]
 
 
 def prefill_flops(runner: ModelRunner, tokens: int, start: int = 0) -> float:
@@ -42,7 +56,7 @@ def prefill_flops(runner: ModelRunner, tokens: int, start: int = 0) -> float:
     p = matrix_params(runner)
     flops = 2.0 * tokens * p["layers"] + 2.0 * p["head"]
     for entry in runner.model.schedule:
-        spec = runner.model.blocks[entry.layer].mixer.spec
+      for spec in _mixer_specs(runner.model.blocks[entry.layer].mixer.spec):
         kind = getattr(spec, "kind", "")
         if kind == "attention":
             # q.k and p.v over the keys the i-th token sees (all start + i of them, or a window's worth): 2 flops per
@@ -52,7 +66,7 @@ def prefill_flops(runner: ModelRunner, tokens: int, start: int = 0) -> float:
             else:
                 pairs = tokens * start + tokens * (tokens + 1) / 2
             flops += 2.0 * pairs * spec.num_heads * (spec.head_dim + getattr(spec, "value_dim", spec.head_dim))
-        elif kind in ("gated_linear_attention", "gated_delta"):
+        elif kind in ("gated_linear_attention", "gated_delta", "decayed_linear_attention"):
             # the matrix state: decay and rank-one update, read-out (and the delta rule's read before the update)
             per = 6.0 if kind == "gated_delta" else 4.0
             flops += per * tokens * spec.num_heads * spec.key_dim * spec.value_dim
@@ -66,7 +80,10 @@ def decode_bytes(runner: ModelRunner, contexts: Sequence[int]) -> float:
     total = float(runner.weight_bytes)
     if runner.model.head is not runner.model.embedding:
         total -= runner.model.embedding.numel() * elem  # an untied embedding is only gathered from
+    views = []
     for view in runner.cache.views:
+        views.extend(view if isinstance(view, tuple) else [view])
+    for view in views:
         spec = getattr(view, "spec", None)
         if spec is None:
             continue
@@ -295,6 +312,70 @@ def bench_linear(m: int, o: int, k: int, mode: str, iters: int = 20) -> dict:
                 tflops=round(2.0 * m * o * k / ms / 1e9, 2))
 
 
+def bench_experts(tokens: int, c: int, f: int, experts: int = 14, identity: int = 2, top: int = 4, groups: int = 4, keep: int = 2,
+                  iters: int = 20) -> dict:
+    """The routed feed-forward's kernels one by one, cold L2, bfloat16: router, sorting the pairs by expert, the grouped
+    gate/up and down products, the weighted gather; beside them the dense SwiGLU feed-forward (gate/up with its
+    activation, then down) of a width that costs a token as many multiply-adds as its real experts do."""
+    from .ops import cuda as ops
+
+    ops.require(ops.libraries_for(torch.bfloat16, ("moe",)))
+    g = torch.Generator(device="cuda").manual_seed(0)
+    outputs = experts + identity
+    h = torch.randn((tokens, c), device="cuda", generator=g).to(torch.bfloat16)
+    w_router = torch.randn((outputs, c), device="cuda", generator=g) * (2.0 / c ** 0.5)
+    correction = torch.randn(outputs, device="cuda", generator=g) * 0.1
+    w_gate_up = (torch.randn((experts, 2 * f, c), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    w_down = (torch.randn((experts, c, f), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    chosen, weights = ops.moe_route(h, w_router, correction, groups, keep, top)
+    real = int((chosen < experts).sum())
+    rows = {"tokens": tokens, "width": c, "expert_width": f, "experts": experts, "identity": identity, "top": top,
+            "real_pairs": real}
+    rows["route_ms"] = round(_time_kernel(lambda: ops.moe_route(h, w_router, correction, groups, keep, top), iters), 5)
+    whole = _time_kernel(lambda: ops.moe_experts(h, w_gate_up, w_down, chosen, weights), iters)
+    rows["experts_ms"] = round(whole, 5)
+    flops = 2.0 * real * 3 * c * f
+    rows["experts_tflops"] = round(flops / whole / 1e9, 1)
+    if tokens * top > ops._MOE_SIMPLE_PAIRS and ops.moe_kernels == "auto":
+        cap = int(ops._fn("moe_grouped", "akas_moe_grouped_rows")(tokens * top, experts))
+        row_of_pair = torch.empty(tokens * top, dtype=torch.int32, device="cuda")
+        tile_expert = torch.empty(cap // 128, dtype=torch.int32, device="cuda")
+        plan = torch.empty(4, dtype=torch.int32, device="cuda")
+        srt = torch.empty((cap, c), dtype=torch.bfloat16, device="cuda")
+        act = torch.zeros((cap, f), dtype=torch.bfloat16, device="cuda")
+        y = torch.empty((cap, c), dtype=torch.float32, device="cuda")
+        out = torch.empty((tokens, c), dtype=torch.float32, device="cuda")
+        st = ops._stream
+        p = lambda t: t.data_ptr()
+        sort = lambda: ops._fn("moe_grouped", "akas_moe_sort")(p(h), c, p(chosen), p(row_of_pair), p(tile_expert), p(plan), p(srt),
+                                                              tokens, top, c, experts, st())
+        gemm = ops._fn("moe_grouped", "akas_moe_grouped_gemm")
+        up = lambda: gemm(p(srt), p(w_gate_up), p(act), p(tile_expert), p(plan), cap, experts, 2 * f, c, 2, st())
+        down = lambda: gemm(p(act), p(w_down), p(y), p(tile_expert), p(plan), cap, experts, c, f, 1, st())
+        comb = lambda: ops._fn("moe_grouped", "akas_moe_combine")(p(h), c, p(y), p(row_of_pair), p(weights), p(out), tokens, top, c, st())
+        sort()
+        for name, fn, work in (("sort_ms", sort, 0.0), ("gate_up_ms", up, 2.0 * real * 2 * c * f), ("down_ms", down, 2.0 * real * c * f),
+                               ("combine_ms", comb, 0.0)):
+            ms = _time_kernel(fn, iters)
+            rows[name] = round(ms, 5)
+            if work:
+                rows[name.replace("_ms", "_tflops")] = round(work / ms / 1e9, 1)
+        rows["grouped_status"] = ops.moe_grouped_status()
+    # the dense feed-forward of equal work per token: width = (real pairs per token) * f
+    dense = max(256, int(round(real / tokens * f / 256)) * 256)
+    w13 = (torch.randn((2 * dense, c), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    w2 = (torch.randn((c, dense), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    res = torch.zeros((tokens, c), device="cuda")
+    mid = ops.linear_swiglu(h, w13)
+    for name, fn, work in (("dense_gate_up_ms", lambda: ops.linear_swiglu(h, w13), 2.0 * tokens * 2 * c * dense),
+                           ("dense_down_ms", lambda: ops.linear(mid, w2, residual=res), 2.0 * tokens * c * dense)):
+        ms = _time_kernel(fn, iters)
+        rows[name] = round(ms, 5)
+        rows[name.replace("_ms", "_tflops")] = round(work / ms / 1e9, 1)
+    rows["dense_width"] = dense
+    return rows
+
+
 def bench_attention(kind: str, batch: int, context: int, heads: int = 32, kv_heads: int = 8, dim: int = 64,
                     page: int = 64, iters: int = 20) -> dict:
     """Paged attention of the bfloat16 path, cold L2. ``decode``: ``batch`` requests of ``context`` cached tokens,
@@ -365,14 +446,33 @@ def gigusun_shape_config(name: str) -> dict:
                 layers=[dict(type=k, mixer=kinds[k], mlp=dict(ff=ff, kind="dense")) for k in order])
 
 
+# Girelix at LFM2's layer sizes: the same width, vocabulary and number of layers. Every layer holds sink attention (half
+# as many query channels as the width, a quarter as many key/value heads as LFM2), linear attention with a constant
+# decay (C / 4 key channels, C / 2 value channels) and 14 experts + 2 identities in 4 groups of which 2 stay, 4 per
+# token, each a quarter as wide as LFM2's feed-forward: a token passes through about as many feed-forward parameters
+# as in LFM2, the model holds 3.5 times as many.
+def girelix_shape_config(name: str) -> dict:
+    lfm2 = config_from_shape(name)
+    c, ff3 = lfm2.hidden_size, lfm2.feed_forward_size
+    left = dict(heads=c // 128, kv_heads=max(1, lfm2.num_key_value_heads // 4), dim=64, vdim=64, scale=0.125,
+                rot=dict(base=1000000.0, dims=64))
+    heads = c // 256
+    right = dict(heads=heads, dim=64, vdim=128, decay=[1.0 - 2.0 ** -(3 + 5 * i / max(1, heads - 1)) for i in range(heads)])
+    mlp = dict(kind="moe", expert=dict(ff=ff3 // 4), router=dict(experts=14, identity=2, top=4, groups=dict(count=4, keep=2)))
+    entry = dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0), mlp=mlp)
+    return dict(architecture="Girelix", width=c, vocab=lfm2.vocab_size, norm=dict(eps=1e-5), residual_mult=0.5,
+                layers=[entry] * len(lfm2.layer_kinds))
+
+
 def config_from_shape(name: str):
     from .config import config_from_dict
 
     return config_from_dict(shape_config(name))
 
 
-def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), steps: int = 64, warmup: int = 4) -> List[dict]:
-    """Gigusun beside LFM2 at equal layer sizes, random weights, bfloat16: milliseconds and tokens a second of a
+def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), steps: int = 64, warmup: int = 4,
+                    designs=("lfm2", "gigusun")) -> List[dict]:
+    """The named designs at equal layer sizes, random weights, bfloat16: milliseconds and tokens a second of a
     ``prompt``-token prefill and of decode steps at each batch size (captured graphs), and the device time of every
     kind of operation in an eager prefill and an eager decode step at the first batch size (CUDA events around each
     call). One row per design."""
@@ -389,7 +489,8 @@ def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), st
         print(f"[compare] {what}", file=sys.stderr, flush=True)
 
     rows = []
-    for design, data in (("lfm2", shape_config(shape)), ("gigusun", gigusun_shape_config(shape))):
+    shapes = {"lfm2": shape_config, "gigusun": gigusun_shape_config, "girelix": girelix_shape_config}
+    for design, data in ((name, shapes[name](shape)) for name in designs):
         say(f"{design} {shape}: writing random weights")
         model_config = config_from_dict(data)
         with tempfile.TemporaryDirectory(prefix="akas-bench-") as folder:
@@ -676,6 +777,14 @@ def _main():
     att.add_argument("--kv-heads", type=int, default=8)
     att.add_argument("--head-dim", type=int, default=64)
     att.add_argument("--iters", type=int, default=20)
+    exp = sub.add_parser("experts", help="the routed feed-forward's kernels beside a dense feed-forward of equal work")
+    exp.add_argument("--tokens", type=int, nargs="+", default=[2048])
+    exp.add_argument("--width", type=int, default=2048)
+    exp.add_argument("--expert-width", type=int, default=2048)
+    exp.add_argument("--experts", type=int, default=14)
+    exp.add_argument("--identity", type=int, default=2)
+    exp.add_argument("--top", type=int, default=4)
+    exp.add_argument("--iters", type=int, default=20)
     srv = sub.add_parser("serving", help="many requests through the engine, prompt portions mixed with decoding")
     srv.add_argument("--shape", default="350m", choices=sorted(SHAPES))
     srv.add_argument("--requests", type=int, default=256)
@@ -712,6 +821,10 @@ def _main():
         return
     if args.what == "long-context":
         print(json.dumps(bench_long_context(args.shape, args.requests, args.prompt, args.generated)))
+        return
+    if args.what == "experts":
+        for n in args.tokens:
+            print(json.dumps(bench_experts(n, args.width, args.expert_width, args.experts, args.identity, args.top, iters=args.iters)))
         return
     if args.what == "attention":
         for b in args.batch:

@@ -13,7 +13,10 @@
 //
 // Packed launches serve steps of single tokens (decoding): a block's rows are then the query heads that share one
 // key/value head, all at the token's position, so its keys and values are read once for the whole group; warps
-// without a live row only help with the copies.
+// without a live row only help with the copies. A packed launch may cut every request's key tiles into `splits`
+// parts (gridDim.z): a block then walks its part only and leaves its unnormalised sums, its maximum and its sum of
+// weights in a scratch buffer, and general_merge_kernel adds the parts (and the sink's term, once) in the order of
+// their numbers: a decode step of a few requests with thousands of keys each fills the GPU that way.
 #include <math.h>
 
 #include "common.cuh"
@@ -58,7 +61,7 @@ __global__ void __launch_bounds__(WARPS * 32, (DKP + DVP <= 192) ? 3 : 2)
 general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_seqlens,
                        const int* __restrict__ positions, bf16* __restrict__ out, Options opt, int page_size, int H, int KH,
-                       int D, int V, int R, int packed, int table) {
+                       int D, int V, int R, int packed, int table, float* __restrict__ partial, int splits) {
   constexpr int KSTRIDE = DKP + 8, VSTRIDE = DVP + 8;  // 16 bytes of padding keep ldmatrix conflict-free
   constexpr int KCH = DKP / 8, VCH = DVP / 8;          // 16-byte chunks per row
   constexpr int KS = DKP / 16;                         // k-steps of Q.K^T
@@ -110,6 +113,12 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   const int kt0 = first_key / BK, kt1 = last_key / BK;
   const int kept_tiles = min((keep + BK - 1) / BK, kt0);  // tiles of kept tokens that lie wholly before the window's first
   const int total = kept_tiles + (kt1 - kt0 + 1);
+  int i_begin = 0, i_end = total;  // the tiles this block walks: all, or its part of them
+  if (splits > 1) {
+    const int per = (total + splits - 1) / splits;
+    i_begin = min(total, (int)blockIdx.z * per);
+    i_end = min(total, i_begin + per);
+  }
   auto tile_of = [&](int i) { return i < kept_tiles ? i : kt0 + (i - kept_tiles); };
 
   auto load_tile = [&](int kt, int stage) {
@@ -141,9 +150,9 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   const int qpos[2] = {packed ? pos0 : pos0 + row2[0], packed ? pos0 : pos0 + row2[1]};
   const int head2[2] = {packed ? kvh * group + min(row2[0], rows - 1) : (int)blockIdx.x,
                         packed ? kvh * group + min(row2[1], rows - 1) : (int)blockIdx.x};
-  const bool sunk = opt.sink || opt.sinks != nullptr;
-  m_run[0] = opt.sinks != nullptr ? opt.sinks[head2[0]] * kLog2e : opt.sink ? 0.f : -INFINITY;
-  m_run[1] = opt.sinks != nullptr ? opt.sinks[head2[1]] * kLog2e : opt.sink ? 0.f : -INFINITY;
+  const bool sunk = splits <= 1 && (opt.sink || opt.sinks != nullptr);  // with parts, the merge adds the sink's term
+  m_run[0] = !sunk ? -INFINITY : opt.sinks != nullptr ? opt.sinks[head2[0]] * kLog2e : 0.f;
+  m_run[1] = !sunk ? -INFINITY : opt.sinks != nullptr ? opt.sinks[head2[1]] * kLog2e : 0.f;
   l_run[0] = l_run[1] = sunk && t == 0 ? 1.f : 0.f;
   const bool biased = opt.r1 != nullptr;
   // r1 ln(1 + r2 d) in units of log2 e is r1 lg2(1 + r2 d): the two factors ln 2 and log2 e cancel
@@ -152,7 +161,7 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   const float inv_cap = opt.cap > 0.f ? 1.f / opt.cap : 0.f;
   const float cap2 = opt.cap * kLog2e, scale2 = opt.scale * kLog2e;
 
-  load_tile(tile_of(0), 0);
+  if (i_begin < i_end) load_tile(tile_of(i_begin), 0);
   if (table > 0) {
     for (int d = tid - kTableBefore; d < table + kTableAfter; d += WARPS * 32)
       penalty[d] = d > 0 ? r1[0] * fast_log2(fmaf(r2[0], (float)d, 1.f)) : 0.f;
@@ -160,10 +169,10 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   }
   const int wlimit = window > 0 ? window : 0x7fffffff;
   const float scale_cap = opt.scale * inv_cap;
-  for (int i = 0; i < total; ++i) {
+  for (int i = i_begin; i < i_end; ++i) {
     const int kt = tile_of(i);
-    const int stage = i & 1;
-    if (i + 1 < total) {
+    const int stage = (i - i_begin) & 1;
+    if (i + 1 < i_end) {
       load_tile(tile_of(i + 1), stage ^ 1);
       cp_async_wait<1>();
     } else {
@@ -268,6 +277,26 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 1);
     l_run[h2] += __shfl_xor_sync(0xffffffffu, l_run[h2], 2);
   }
+  if (splits > 1) {
+    // this part's sums as they stand, per (token, head, part): V unnormalised channels, the maximum, the sum of weights
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      const int row = warp * 16 + g + h2 * 8;
+      if (row >= rows) continue;
+      float* dst = partial + (((size_t)q0 * H + head2[h2]) * splits + blockIdx.z) * (V + 2);
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+        if (nb * 8 + 2 * t < V) {
+          dst[nb * 8 + 2 * t] = o[nb][h2 * 2];
+          dst[nb * 8 + 2 * t + 1] = o[nb][h2 * 2 + 1];
+        }
+      if (t == 0) {
+        dst[V] = m_run[h2];
+        dst[V + 1] = l_run[h2];
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int h2 = 0; h2 < 2; ++h2) {
     const int row = warp * 16 + g + h2 * 8;
@@ -284,10 +313,37 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
   }
 }
 
+// One block per (request of one token, head): the parts' sums, rescaled to the common maximum (the sink's logit
+// included), added in the order of the parts; then the division, the gate and the constant.
+__global__ void general_merge_kernel(const float* __restrict__ partial, const int* __restrict__ cu_seqlens, bf16* __restrict__ out,
+                                     Options opt, int H, int V, int splits) {
+  const int token = cu_seqlens[blockIdx.x], head = blockIdx.y;
+  const float* src = partial + ((size_t)token * H + head) * splits * (V + 2);
+  const bool sunk = opt.sink || opt.sinks != nullptr;
+  const float sink2 = opt.sinks != nullptr ? opt.sinks[head] * kLog2e : 0.f;
+  float top = sunk ? sink2 : -INFINITY;
+  for (int z = 0; z < splits; ++z) top = fmaxf(top, src[(size_t)z * (V + 2) + V]);
+  float denom = sunk ? exp2f(sink2 - top) : 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float m = src[(size_t)z * (V + 2) + V];
+    if (m != -INFINITY) denom += src[(size_t)z * (V + 2) + V + 1] * exp2f(m - top);
+  }
+  float inv = denom > 0.f ? opt.out_scale / denom : 0.f;
+  if (opt.gate != nullptr) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[(size_t)token * opt.ldg + head])));
+  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < splits; ++z) {
+      const float m = src[(size_t)z * (V + 2) + V];
+      if (m != -INFINITY) acc = fmaf(src[(size_t)z * (V + 2) + c], exp2f(m - top), acc);
+    }
+    out[(size_t)token * opt.ldo + (size_t)head * V + c] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
 template <int DKP, int DVP>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* block_table, int max_blocks,
            const int* cu_seqlens, const int* positions, void* out, const Options& opt, int page_size, int tiles, int H,
-           int KH, int D, int V, int R, int packed, cudaStream_t stream) {
+           int KH, int D, int V, int R, int packed, float* partial, int splits, cudaStream_t stream) {
   // the table of distance penalties: for unpacked launches (one head a block) with a window of at most kTableMost keys
   constexpr int kTableMost = 8192;
   const int table = !packed && opt.r1 != nullptr && opt.window > 0 && opt.window <= kTableMost ? opt.window : 0;
@@ -302,9 +358,12 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const int* blo
     if (e != cudaSuccess) return (int)e;
     configured[device] = true;
   }
-  return launch_ordinary(general_prefill_kernel<DKP, DVP>, dim3(packed ? KH : H, tiles), dim3(WARPS * 32), (size_t)smem, stream,
-                        (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks, cu_seqlens, positions,
-                        (bf16*)out, opt, page_size, H, KH, D, V, R, packed, table);
+  const int err = launch_ordinary(general_prefill_kernel<DKP, DVP>, dim3(packed ? KH : H, tiles, splits), dim3(WARPS * 32), (size_t)smem,
+                                  stream, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_table, max_blocks,
+                                  cu_seqlens, positions, (bf16*)out, opt, page_size, H, KH, D, V, R, packed, table, partial, splits);
+  if (err || splits <= 1) return err;
+  return launch_ordinary(general_merge_kernel, dim3(R, H), dim3(V >= 128 ? 128 : 64), 0, stream, (const float*)partial, cu_seqlens,
+                         (bf16*)out, opt, H, V, splits);
 }
 
 }  // namespace
@@ -319,10 +378,12 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
                                        int max_blocks, const int* cu_seqlens, const int* positions, void* out, float scale,
                                        int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                        const void* gate, long long ldg, int page_size, int tiles, int H, int KH, int D, int V,
-                                       int R, int packed, const float* sinks, float out_scale, long long ldo,
-                                       cudaStream_t stream) {
+                                       int R, int packed, const float* sinks, float out_scale, long long ldo, float* partial,
+                                       int splits, cudaStream_t stream) {
   if (!akas_attention_general_tc_takes(D, V)) return 3999;
   if (ldo % 2) return 3999;
+  // parts: packed launches only; partial holds (first token of the launch + R) * H * splits * (V + 2) floats
+  if (splits < 1 || splits > 64 || (splits > 1 && (!packed || partial == nullptr))) return (int)cudaErrorInvalidValue;
   if (packed && (KH <= 0 || H / KH > BQ || tiles != R)) return 3999;
   if (KH <= 0 || H % KH || tiles > 65535 || R <= 0) return (int)cudaErrorInvalidValue;
   if (tiles <= 0) return 0;
@@ -331,7 +392,7 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
 #define AKAS_TC(A, B)                                                                                                   \
   if (dk == A && dv == B)                                                                                               \
     return launch<A * 32, B * 32>(q, k_pool, v_pool, block_table, max_blocks, cu_seqlens, positions, out, opt, page_size, \
-                                  tiles, H, KH, D, V, R, packed, stream);
+                                  tiles, H, KH, D, V, R, packed, partial, splits, stream);
   AKAS_TC(1, 1) AKAS_TC(1, 2) AKAS_TC(1, 3) AKAS_TC(1, 4)
   AKAS_TC(2, 1) AKAS_TC(2, 2) AKAS_TC(2, 3) AKAS_TC(2, 4)
   AKAS_TC(3, 1) AKAS_TC(3, 2) AKAS_TC(3, 3) AKAS_TC(3, 4)

@@ -260,7 +260,8 @@ AKAS_API int akas_add_rows(float* h, const void* table, const int* index, int N,
 
 // x[n, c] += mult * (ls_a[c] * a[n, c] + ls_b[c] * b[n, c]) in place on the float32 residual stream: the update of a
 // block whose sublayers all read one norm of x and whose results meet, each through a learned scale per channel,
-// in one sum. b (and ls_b) may be null: a block without the second sublayer. Four channels a thread where C allows.
+// in one sum. b may be null: a block without the second sublayer; a null scale is all ones. Four channels a thread
+// where C allows.
 __global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ ls_a,
                                   const float* __restrict__ b, const float* __restrict__ ls_b, float mult, long long total,
                                   int C, int vec) {
@@ -269,18 +270,19 @@ __global__ void scaled_add_kernel(float* __restrict__ x, const float* __restrict
   if (vec) {
     const int c = (int)(i % C);
     float4 xv = *reinterpret_cast<float4*>(x + i);
-    const float4 av = *reinterpret_cast<const float4*>(a + i), la = *reinterpret_cast<const float4*>(ls_a + c);
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 av = *reinterpret_cast<const float4*>(a + i), la = ls_a ? *reinterpret_cast<const float4*>(ls_a + c) : one;
     float4 sum = make_float4(la.x * av.x, la.y * av.y, la.z * av.z, la.w * av.w);
     if (b != nullptr) {
-      const float4 bv = *reinterpret_cast<const float4*>(b + i), lb = *reinterpret_cast<const float4*>(ls_b + c);
+      const float4 bv = *reinterpret_cast<const float4*>(b + i), lb = ls_b ? *reinterpret_cast<const float4*>(ls_b + c) : one;
       sum.x = fmaf(lb.x, bv.x, sum.x); sum.y = fmaf(lb.y, bv.y, sum.y); sum.z = fmaf(lb.z, bv.z, sum.z); sum.w = fmaf(lb.w, bv.w, sum.w);
     }
     xv.x = fmaf(mult, sum.x, xv.x); xv.y = fmaf(mult, sum.y, xv.y); xv.z = fmaf(mult, sum.z, xv.z); xv.w = fmaf(mult, sum.w, xv.w);
     *reinterpret_cast<float4*>(x + i) = xv;
   } else {
     const int c = (int)(i % C);
-    float sum = ls_a[c] * a[i];
-    if (b != nullptr) sum = fmaf(ls_b[c], b[i], sum);
+    float sum = (ls_a ? ls_a[c] : 1.f) * a[i];
+    if (b != nullptr) sum = fmaf(ls_b ? ls_b[c] : 1.f, b[i], sum);
     x[i] = fmaf(mult, sum, x[i]);
   }
 }

@@ -19,7 +19,7 @@ using namespace akas;
 namespace {
 
 constexpr int kRouteTokens = 8;   // tokens of a router block = its warps
-constexpr int kRouteChunk = 512;  // channels of h staged at a time
+constexpr int kRouteChunk = 2048; // channels of h staged at a time (64 KB of float32 rows for the block's tokens)
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 
@@ -27,7 +27,7 @@ template <typename T>
 __global__ void __launch_bounds__(kRouteTokens * 32)
 moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ w, const float* __restrict__ correction,
                  int* __restrict__ chosen, float* __restrict__ weights, int N, int C, int R, int groups, int keep, int top) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   float* rows = smem;                              // [kRouteTokens][kRouteChunk]
   float* z = rows + kRouteTokens * kRouteChunk;    // [kRouteTokens][R] logits, then scores
   float* pick = z + kRouteTokens * R;              // [kRouteTokens][R] choice scores
@@ -38,19 +38,47 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
   for (int c0 = 0; c0 < C; c0 += kRouteChunk) {
     const int width = min(kRouteChunk, C - c0);
     __syncthreads();
-    for (int i = threadIdx.x; i < kRouteTokens * width; i += blockDim.x) {
-      const int t = i / width, c = i % width;
-      rows[t * kRouteChunk + c] = n0 + t < N ? to_f32(h[(size_t)(n0 + t) * ldh + c0 + c]) : 0.f;
+    if (C % 8 == 0 && ldh % 8 == 0 && ((uintptr_t)h % 16) == 0) {  // eight channels a load
+      const int per_row = width / 8;
+      for (int i = threadIdx.x; i < kRouteTokens * per_row; i += blockDim.x) {
+        const int t = i / per_row, c = (i % per_row) * 8;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (n0 + t < N) load8(h + (size_t)(n0 + t) * ldh + c0 + c, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) rows[t * kRouteChunk + c + j] = v[j];
+      }
+    } else {
+      for (int i = threadIdx.x; i < kRouteTokens * width; i += blockDim.x) {
+        const int t = i / width, c = i % width;
+        rows[t * kRouteChunk + c] = n0 + t < N ? to_f32(h[(size_t)(n0 + t) * ldh + c0 + c]) : 0.f;
+      }
     }
     __syncthreads();
+    // a warp takes every eighth router output: its row of w once, 16 bytes a lane and several loads in flight, against
+    // the block's token rows in shared memory; the order of a (token, output) sum depends on the width only
+    const bool vec = C % 4 == 0 && ((uintptr_t)w % 16) == 0;
     for (int e = warp; e < R; e += kRouteTokens) {
       float acc[kRouteTokens];
 #pragma unroll
       for (int t = 0; t < kRouteTokens; ++t) acc[t] = 0.f;
-      for (int c = lane; c < width; c += 32) {
-        const float wv = w[(size_t)e * C + c0 + c];
+      const float* wr = w + (size_t)e * C + c0;
+      if (vec) {
+#pragma unroll 4
+        for (int c = lane * 4; c < width; c += 128) {
+          const float4 wv = *reinterpret_cast<const float4*>(wr + c);
 #pragma unroll
-        for (int t = 0; t < kRouteTokens; ++t) acc[t] = fmaf(rows[t * kRouteChunk + c], wv, acc[t]);
+          for (int t = 0; t < kRouteTokens; ++t) {
+            const float4 hv = *reinterpret_cast<const float4*>(rows + t * kRouteChunk + c);
+            acc[t] = fmaf(hv.x, wv.x, acc[t]); acc[t] = fmaf(hv.y, wv.y, acc[t]);
+            acc[t] = fmaf(hv.z, wv.z, acc[t]); acc[t] = fmaf(hv.w, wv.w, acc[t]);
+          }
+        }
+      } else {
+        for (int c = lane; c < width; c += 32) {
+          const float wv = wr[c];
+#pragma unroll
+          for (int t = 0; t < kRouteTokens; ++t) acc[t] = fmaf(rows[t * kRouteChunk + c], wv, acc[t]);
+        }
       }
 #pragma unroll
       for (int t = 0; t < kRouteTokens; ++t) {
@@ -236,7 +264,8 @@ AKAS_API int akas_moe_gate_up(const void* h, long long ldh, const void* w_gate_u
                               int top, int C, int F, int experts, int dtype, cudaStream_t stream) {
   if (N <= 0 || top <= 0 || experts <= 0) return 0;
   const int pairs = N * top;
-  const dim3 grid(pairs, max(1, min((F + 7) / 8, pairs >= 4096 ? 2 : 16)));
+  // warps enough to fill the GPU when the pairs are few (a row of F per warp), fewer and longer-lived when they are many
+  const dim3 grid(pairs, max(1, min((F + 7) / 8, pairs >= 4096 ? 2 : pairs >= 256 ? 16 : 256)));
   if (dtype == AKAS_F32)
     return launch_ordinary(moe_gate_up_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, ldh, (const float*)w_gate_up,
                            chosen, (float*)act, pairs, top, C, F, experts);
@@ -248,7 +277,7 @@ AKAS_API int akas_moe_down(const void* h, long long ldh, const void* w_down, con
                            const void* act, float* out, int N, int top, int C, int F, int experts, int dtype,
                            cudaStream_t stream) {
   if (N <= 0) return 0;
-  const dim3 grid(N, max(1, min((C + 7) / 8, N >= 2048 ? 2 : 32)));
+  const dim3 grid(N, max(1, min((C + 7) / 8, N >= 2048 ? 2 : N >= 64 ? 32 : 256)));
   if (dtype == AKAS_F32)
     return launch_ordinary(moe_down_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, ldh, (const float*)w_down, chosen,
                            weights, (const float*)act, out, top, C, F, experts);

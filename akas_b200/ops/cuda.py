@@ -75,7 +75,8 @@ _SIGNATURES = {
     "attention_general_tc": {
         "akas_attention_general_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
                                       c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int,
-                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p, c_int,
+                                      c_void_p],
         "akas_attention_general_tc_takes": [c_int, c_int],
     },
     "moe_grouped": {
@@ -1316,6 +1317,9 @@ if general_attention not in ("mma", "plain"):
     raise ValueError(f"AKAS_B200_GENERAL_ATTENTION must be mma or plain, got {general_attention!r}")
 
 
+general_splits = os.environ.get("AKAS_B200_GENERAL_SPLITS", "1") != "0"  # 0: a decoding request's keys are never cut into parts
+
+
 @_flushes
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
                       r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0):
@@ -1350,10 +1354,14 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
             launches.append((first, len(lens) - first, tiles, 0))
         if launches and all(0 < tiles <= 65535 for _, _, tiles, _ in launches):
             for start, requests, tiles, packed in launches:
+                # single tokens: every request's keys in parts, so that a few requests with long pasts fill the GPU; the
+                # parts' sums meet in a merge kernel (the count comes from sizes the host knows, as for the plain decode path)
+                splits = decode_splits(requests, kh, 1, getattr(ctx, "max_context", 0) or 0) if packed and general_splits else 1
+                partial = torch.empty(requests * heads * splits * (vd + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
                 err = _fn("attention_general_tc", "akas_attention_general_tc")(
                     _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table[start:]), block_table.shape[1],
                     _ptr(ctx.cu_seqlens[start:]), _ptr(positions), op, *options, tiles, heads, kh, d, vd, requests,
-                    packed, *tail, _stream())
+                    packed, *tail, _ptr(partial), splits, _stream())
                 _check(err, "attention_general (tensor cores)")
             singles = 0
     if singles:
@@ -1441,16 +1449,6 @@ def moe_experts(h, w_gate_up, w_down, chosen, weights):
     return out
 
 
-_ones = {}
-
-
-def _ones_like_row(c: int, device):
-    t = _ones.get((c, device))
-    if t is None:
-        t = _ones[(c, device)] = torch.ones(c, dtype=torch.float32, device=device)
-    return t
-
-
 @_flushes
 def scaled_add(x, a, scale_a, b, scale_b, mult):
     """x += mult * (scale_a * a + scale_b * b) in place on float32 x [N, C]; scales float32 [C] (None: ones); b may be None."""
@@ -1458,9 +1456,6 @@ def scaled_add(x, a, scale_a, b, scale_b, mult):
     for t in (x, a) + ((b,) if b is not None else ()):
         if t.dtype != torch.float32 or t.shape != (n, c) or not t.is_contiguous():
             raise ValueError("scaled_add takes dense float32 tensors [N, C]")
-    scale_a = _ones_like_row(c, x.device) if scale_a is None else scale_a
-    if b is not None and scale_b is None:
-        scale_b = _ones_like_row(c, x.device)
     _check(_fn("elementwise", "akas_scaled_add")(_ptr(x), _ptr(a), _ptr(scale_a), _ptr(b), _ptr(scale_b) if b is not None else None,
                                                 float(mult), n, c, _stream()), "scaled_add")
     return x

@@ -599,7 +599,8 @@ def test_sink_attention_kernels(heads, kv_heads, dim, rot, page, dtype):
         page_of = table[1, 44 // page].item()
         assert torch.equal(pools[1][1][page_of, :, 44 % page].reshape(-1), k[45])
     sinks = (torch.randn(heads, generator=g) * 2.0).cuda()
-    ctx = SimpleNamespace(query_lens=tuple(lengths), decode_only=False, cu_seqlens=cu)
+    # (the largest context lets the decoding request at the step's front have its keys cut into parts)
+    ctx = SimpleNamespace(query_lens=tuple(lengths), decode_only=False, cu_seqlens=cu, max_context=400)
     want = reference.attention_general(qn[0], *pools[0], table, seq, pos, 0.3, None, 0, 0.0, None, None, False, None, page,
                                        sinks=sinks, out_scale=1.2)
     none = reference.attention_general(qn[0], *pools[0], table, seq, pos, 0.3, None, 0, 0.0, None, None, False, None, page)
@@ -611,3 +612,13 @@ def test_sink_attention_kernels(heads, kv_heads, dim, rot, page, dtype):
                                      sinks=sinks, out=view, out_scale=1.2)
         assert got is view and float(wide[:, :8].abs().max()) == 0.0 and float(wide[:, 8 + heads * dim :].abs().max()) == 0.0
         _close(view, want, 2e-5 if dtype == torch.float32 else 1.5e-2, f"attention with sinks {layout is None}")
+    # a step of single tokens with long pasts: keys in parts, merged; against the same step without parts
+    singles = [399, 130, 64, 257]
+    pos1 = torch.tensor(singles, dtype=torch.int32).cuda()
+    cu1, seq1, _ = _batch([1, 1, 1, 1], [0, 1, 2, 3], "cuda")
+    q1 = qn[0][:4].contiguous()
+    want1 = reference.attention_general(q1, *pools[0], table, seq1, pos1, 0.3, None, 0, 0.0, None, None, False, None, page, sinks=sinks)
+    for most in (0, 400):
+        ctx1 = SimpleNamespace(query_lens=(1, 1, 1, 1), decode_only=True, cu_seqlens=cu1, max_context=most)
+        got1 = cuda.attention_general(q1, *pools[0], table, seq1, pos1, 0.3, None, 0, 0.0, None, None, False, None, page, ctx1, sinks=sinks)
+        _close(got1, want1, 2e-5 if dtype == torch.float32 else 1.5e-2, f"single tokens, keys in parts: {most > 0}")
