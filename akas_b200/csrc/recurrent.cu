@@ -264,6 +264,245 @@ int launch_scan(const T* q, long long ldq, const T* k, long long ldk, const T* v
 #undef AKAS_SCAN
 }
 
+// ------------------------------------------------------------------------------------------------ fixed decay, in chunks
+//
+// The recurrence with one constant decay per head, S <- a S + k v^T, o = S^T q, for prompt portions: a request's
+// tokens of this step are cut into chunks of kChunk, and three kernels replace the walk token by token.
+//   chunk_state   per (chunk, head, tile of value channels): U = sum_s a^(len - 1 - s) v_s k_s^T, what the chunk's
+//                 tokens add to the state by the chunk's end;
+//   chunk_carry   per (request, head): S_0 = the slot's state; the state at every chunk's start, S_(j+1) = a^len_j S_j
+//                 + U_j, written where U_j stood; the last one back to the slot;
+//   chunk_output  per (chunk, head, tile of value channels): o_t = a^(t + 1) S_j^T q_t + sum_(s <= t) a^(t - s) (q_t . k_s) v_s.
+// Everything is float32 fused multiply-adds (the decays' powers come from a float64 pow, rounded once); sums run in
+// a fixed order that depends on where a chunk starts in the step, so a result differs from the token-by-token
+// kernel's, and between ways of cutting a prompt, by rounding only. Key sizes up to kChunkMaxD.
+constexpr int kChunk = 64, kChunkVT = 64, kChunkMaxD = 128, kChunkThreads = 256;
+
+// which (request, chunk of it) the block's chunk number is; false if there is none
+__device__ __forceinline__ bool find_chunk(const int* __restrict__ cu_seqlens, const int* __restrict__ slots, int R, int id,
+                                           int& req, int& first, int& len, int& index) {
+  for (int r = 0; r < R; ++r) {
+    const int b = cu_seqlens[r], e = cu_seqlens[r + 1];
+    const int chunks = slots[r] < 0 ? 0 : (e - b + kChunk - 1) / kChunk;
+    if (id < chunks) {
+      req = r; index = id; first = b + id * kChunk; len = min(kChunk, e - first);
+      return true;
+    }
+    id -= chunks;
+  }
+  return false;
+}
+
+template <typename T>
+__device__ __forceinline__ float chunk_in(const T* p, int act) {
+  const float x = to_f32(*p);
+  return act ? x * sigmoid_f(x) : x;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads)
+chunk_state_kernel(const T* __restrict__ k, long long ldk, const T* __restrict__ v, long long ldv, const float* __restrict__ decay,
+                   const int* __restrict__ cu_seqlens, const int* __restrict__ slots, float* __restrict__ scratch, int R, int H,
+                   int D, int V, int DP, int act) {
+  extern __shared__ __align__(16) float sm[];
+  float* sk = sm;                    // [kChunk][DP]
+  float* sv = sk + kChunk * DP;      // [kChunk][kChunkVT], already times a^(len - 1 - s)
+  int req, first, len, index;
+  if (!find_chunk(cu_seqlens, slots, R, blockIdx.x, req, first, len, index)) return;
+  const int h = blockIdx.y, v0 = blockIdx.z * kChunkVT;
+  const double a = (double)decay[h];
+  for (int i = threadIdx.x; i < kChunk * DP; i += kChunkThreads) {
+    const int t = i / DP, d = i % DP;
+    sk[i] = t < len && d < D ? chunk_in(k + (size_t)(first + t) * ldk + (size_t)h * D + d, act) : 0.f;
+  }
+  for (int i = threadIdx.x; i < kChunk * kChunkVT; i += kChunkThreads) {
+    const int t = i / kChunkVT, c = v0 + i % kChunkVT;
+    sv[i] = t < len && c < V ? chunk_in(v + (size_t)(first + t) * ldv + (size_t)h * V + c, act) * (float)pow(a, (double)(len - 1 - t)) : 0.f;
+  }
+  __syncthreads();
+  // a thread owns 4 value channels x 4 key channels at a time
+  const int tv = (threadIdx.x / 16) * 4, td = (threadIdx.x % 16) * 4;  // 16 x 16 threads cover 64 x 64
+  float* out = scratch + ((size_t)blockIdx.x * H + h) * V * D;
+  for (int d0 = 0; d0 < DP; d0 += 64) {
+    float acc[4][4] = {};
+    if (d0 + td < DP) {
+      for (int t = 0; t < kChunk; ++t) {
+        const float4 kv = *reinterpret_cast<const float4*>(sk + t * DP + d0 + td);
+        const float4 vv = *reinterpret_cast<const float4*>(sv + t * kChunkVT + tv);
+        const float kk[4] = {kv.x, kv.y, kv.z, kv.w}, vs[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(vs[i], kk[j], acc[i][j]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (v0 + tv + i < V && d0 + td + j < D) out[(size_t)(v0 + tv + i) * D + d0 + td + j] = acc[i][j];
+  }
+}
+
+// One block per (request, head): walks the request's chunks; every element of the state is one thread's chain.
+__global__ void chunk_carry_kernel(const float* __restrict__ decay, float* __restrict__ state, long long slot_stride,
+                                   const int* __restrict__ cu_seqlens, const int* __restrict__ slots, float* __restrict__ scratch,
+                                   int R, int H, int D, int V, int write) {
+  const int req = blockIdx.x, h = blockIdx.y;
+  const int slot = slots[req];
+  if (slot < 0) return;
+  int base = 0;  // the number of the request's first chunk
+  for (int r = 0; r < req; ++r) base += slots[r] < 0 ? 0 : (cu_seqlens[r + 1] - cu_seqlens[r] + kChunk - 1) / kChunk;
+  const int n = cu_seqlens[req + 1] - cu_seqlens[req];
+  const int chunks = (n + kChunk - 1) / kChunk;
+  if (chunks == 0) return;
+  const double a = (double)decay[h];
+  const float whole = (float)pow(a, (double)kChunk), last = (float)pow(a, (double)(n - (chunks - 1) * kChunk));
+  float* srow = state + (size_t)slot * slot_stride + (size_t)h * V * D;
+  for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < V * D; i += gridDim.z * blockDim.x) {
+    float s = srow[i];
+    for (int j0 = 0; j0 < chunks; j0 += 8) {  // eight chunks' sums are fetched at once: the chain itself waits for no load
+      float add[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) add[e] = j0 + e < chunks ? scratch[((size_t)(base + j0 + e) * H + h) * V * D + i] : 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (j0 + e < chunks) {
+          scratch[((size_t)(base + j0 + e) * H + h) * V * D + i] = s;
+          s = fmaf(j0 + e + 1 < chunks ? whole : last, s, add[e]);
+        }
+      }
+    }
+    if (write) srow[i] = s;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads)
+chunk_output_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk, const T* __restrict__ v,
+                    long long ldv, const float* __restrict__ decay, const int* __restrict__ cu_seqlens,
+                    const int* __restrict__ slots, const float* __restrict__ scratch, float* __restrict__ out, int R, int H, int D,
+                    int V, int DP, float q_scale, int act) {
+  extern __shared__ __align__(16) float sm[];
+  float* sq = sm;                        // [kChunk][DP]
+  float* sk = sq + kChunk * DP;          // [kChunk][DP]
+  float* ss = sk + kChunk * DP;          // [kChunkVT][DP] the state at the chunk's start (rows: value channels)
+  float* sv = ss + kChunkVT * DP;        // [kChunk][kChunkVT]
+  float* sa = sv + kChunk * kChunkVT;    // [kChunk][kChunk] decayed scores, zero above the diagonal
+  float* pw = sa + kChunk * kChunk;      // [kChunk + 1] powers of the decay
+  int req, first, len, index;
+  if (!find_chunk(cu_seqlens, slots, R, blockIdx.x, req, first, len, index)) return;
+  const int h = blockIdx.y, v0 = blockIdx.z * kChunkVT;
+  const double a = (double)decay[h];
+  for (int i = threadIdx.x; i <= kChunk; i += kChunkThreads) pw[i] = (float)pow(a, (double)i);
+  for (int i = threadIdx.x; i < kChunk * DP; i += kChunkThreads) {
+    const int t = i / DP, d = i % DP;
+    const bool in = t < len && d < D;
+    sq[i] = in ? chunk_in(q + (size_t)(first + t) * ldq + (size_t)h * D + d, act) * q_scale : 0.f;
+    sk[i] = in ? chunk_in(k + (size_t)(first + t) * ldk + (size_t)h * D + d, act) : 0.f;
+  }
+  const float* start = scratch + ((size_t)blockIdx.x * H + h) * V * D;
+  for (int i = threadIdx.x; i < kChunkVT * DP; i += kChunkThreads) {
+    const int c = v0 + i / DP, d = i % DP;
+    ss[i] = c < V && d < D ? start[(size_t)c * D + d] : 0.f;
+  }
+  for (int i = threadIdx.x; i < kChunk * kChunkVT; i += kChunkThreads) {
+    const int t = i / kChunkVT, c = v0 + i % kChunkVT;
+    sv[i] = t < len && c < V ? chunk_in(v + (size_t)(first + t) * ldv + (size_t)h * V + c, act) : 0.f;
+  }
+  __syncthreads();
+  const int tr = (threadIdx.x / 16) * 4, tc = (threadIdx.x % 16) * 4;  // a thread's 4 rows x 4 columns of a 64 x 64 result
+  {  // scores of queries tr.. against keys tc.., times a^(t - s) on and below the diagonal
+    float acc[4][4] = {};
+    if (tc <= tr + 3) {
+      for (int d = 0; d < DP; d += 4) {
+        float4 qv[4], kv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          qv[i] = *reinterpret_cast<const float4*>(sq + (tr + i) * DP + d);
+          kv[i] = *reinterpret_cast<const float4*>(sk + (tc + i) * DP + d);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            acc[i][j] = fmaf(qv[i].x, kv[j].x, acc[i][j]); acc[i][j] = fmaf(qv[i].y, kv[j].y, acc[i][j]);
+            acc[i][j] = fmaf(qv[i].z, kv[j].z, acc[i][j]); acc[i][j] = fmaf(qv[i].w, kv[j].w, acc[i][j]);
+          }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) sa[(tr + i) * kChunk + tc + j] = tc + j <= tr + i ? acc[i][j] * pw[tr + i - tc - j] : 0.f;
+  }
+  __syncthreads();
+  float acc[4][4] = {};  // tokens tr.. x value channels tc..
+  for (int t = 0; t < min(tr + 4, len); ++t) {  // keys up to the thread's last query
+    const float4 vv = *reinterpret_cast<const float4*>(sv + t * kChunkVT + tc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float w = sa[(tr + i) * kChunk + t];
+      acc[i][0] = fmaf(w, vv.x, acc[i][0]); acc[i][1] = fmaf(w, vv.y, acc[i][1]);
+      acc[i][2] = fmaf(w, vv.z, acc[i][2]); acc[i][3] = fmaf(w, vv.w, acc[i][3]);
+    }
+  }
+  float carry[4][4] = {};  // what the state at the chunk's start gives: S^T q, times a^(t + 1) below
+  for (int d = 0; d < DP; d += 4) {
+    float4 qv[4], sr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      qv[i] = *reinterpret_cast<const float4*>(sq + (tr + i) * DP + d);
+      sr[i] = *reinterpret_cast<const float4*>(ss + (tc + i) * DP + d);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        carry[i][j] = fmaf(qv[i].x, sr[j].x, carry[i][j]); carry[i][j] = fmaf(qv[i].y, sr[j].y, carry[i][j]);
+        carry[i][j] = fmaf(qv[i].z, sr[j].z, carry[i][j]); carry[i][j] = fmaf(qv[i].w, sr[j].w, carry[i][j]);
+      }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (tr + i < len && v0 + tc + j < V)
+        out[(size_t)(first + tr + i) * ((size_t)H * V) + (size_t)h * V + v0 + tc + j] = fmaf(pw[tr + i + 1], carry[i][j], acc[i][j]);
+}
+
+template <typename T>
+int launch_chunks(const T* q, long long ldq, const T* k, long long ldk, const T* v, long long ldv, const float* decay, float* state,
+                  long long slot_stride, const int* cu_seqlens, const int* slots, float* out, float* scratch, int tokens,
+                  int requests, int H, int D, int V, float q_scale, int act, int write, cudaStream_t stream) {
+  const int DP = (D + 3) / 4 * 4 + 4;  // rows of key channels in shared memory: whole 16-byte words, and a pad against bank conflicts
+  const int chunks = (tokens + kChunk - 1) / kChunk + requests;  // at most: every request may end with a part of a chunk
+  const int vt = (V + kChunkVT - 1) / kChunkVT;
+  const size_t smem1 = sizeof(float) * ((size_t)kChunk * DP + kChunk * kChunkVT);
+  const size_t smem3 = sizeof(float) * ((size_t)2 * kChunk * DP + (size_t)kChunkVT * DP + kChunk * kChunkVT + kChunk * kChunk + kChunk + 4);
+  static bool configured[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+  if (!configured[device]) {
+    const int most = (int)(sizeof(float) * ((size_t)2 * kChunk * (kChunkMaxD + 4) + (size_t)kChunkVT * (kChunkMaxD + 4) + kChunk * kChunkVT +
+                                           kChunk * kChunk + kChunk + 4));
+    cudaError_t e = cudaFuncSetAttribute(chunk_output_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(chunk_output_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(chunk_state_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(chunk_state_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (e != cudaSuccess) return (int)e;
+    configured[device] = true;
+  }
+  int err = launch_ordinary(chunk_state_kernel<T>, dim3(chunks, H, vt), dim3(kChunkThreads), smem1, stream, k, ldk, v, ldv, decay,
+                            cu_seqlens, slots, scratch, requests, H, D, V, DP, act);
+  if (err) return err;
+  err = launch_ordinary(chunk_carry_kernel, dim3(requests, H, min(64, (V * D + 255) / 256)), dim3(256), 0, stream, decay, state,
+                        slot_stride, cu_seqlens, slots, scratch, requests, H, D, V, write);
+  if (err) return err;
+  return launch_ordinary(chunk_output_kernel<T>, dim3(chunks, H, vt), dim3(kChunkThreads), smem3, stream, q, ldq, k, ldk, v, ldv, decay,
+                         cu_seqlens, slots, (const float*)scratch, out, requests, H, D, V, DP, q_scale, act);
+}
+
 // ------------------------------------------------------------------------------------------------ causal convolution
 //
 // y[n, c] = silu(sum_j taps[c, j] * x_(i - L + 1 + j)) for the i-th token of its request in this step; inputs before
@@ -464,6 +703,26 @@ AKAS_API int akas_decay_scan(const void* q, long long ldq, const void* k, long l
   return launch_scan<bf16, false, true>((const bf16*)q, ldq, (const bf16*)k, ldk, (const bf16*)v, ldv, decay, nullptr, state,
                                         slot_stride, cu_seqlens, slots, out, tokens, requests, H, 1, D, V, q_scale, write,
                                         stream, act);
+}
+
+// Floats of scratch that akas_decay_scan_chunked needs; 0 where it does not take the sizes (the token-by-token kernel does).
+AKAS_API long long akas_decay_chunk_scratch(int tokens, int requests, int H, int D, int V) {
+  if (D > kChunkMaxD || tokens <= 0 || requests <= 0) return 0;
+  return (long long)((tokens + kChunk - 1) / kChunk + requests) * H * D * V;
+}
+
+// The same recurrence as akas_decay_scan, in chunks (see above): for steps that bring many tokens a request.
+AKAS_API int akas_decay_scan_chunked(const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
+                                     const float* decay, float* state, long long slot_stride, const int* cu_seqlens,
+                                     const int* slots, float* out, float* scratch, int tokens, int requests, int H, int D, int V,
+                                     float q_scale, int act, int write, int dtype, cudaStream_t stream) {
+  if (tokens <= 0 || requests <= 0 || H <= 0) return 0;
+  if (D > kChunkMaxD || scratch == nullptr) return (int)cudaErrorInvalidValue;
+  if (dtype == AKAS_F32)
+    return launch_chunks((const float*)q, ldq, (const float*)k, ldk, (const float*)v, ldv, decay, state, slot_stride, cu_seqlens,
+                         slots, out, scratch, tokens, requests, H, D, V, q_scale, act, write, stream);
+  return launch_chunks((const bf16*)q, ldq, (const bf16*)k, ldk, (const bf16*)v, ldv, decay, state, slot_stride, cu_seqlens, slots,
+                       out, scratch, tokens, requests, H, D, V, q_scale, act, write, stream);
 }
 
 AKAS_API int akas_delta_scan(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,

@@ -60,6 +60,10 @@ _SIGNATURES = {
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_gated_rmsnorm": [c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_float, c_longlong, c_void_p],
+        "akas_decay_chunk_scratch": [c_int, c_int, c_int, c_int, c_int],
+        "akas_decay_scan_chunked": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
+                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                    c_int, c_void_p],
         "akas_decay_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong,
                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                             c_void_p],
@@ -186,6 +190,7 @@ _SIGNATURES = {
     },
 }
 
+_RESTYPES = {"akas_decay_chunk_scratch": c_longlong}  # everything else returns an int (an error code or a small answer)
 _functions = {}
 
 
@@ -240,7 +245,7 @@ def _bind(lib_name: str) -> None:
         if fn_name not in _functions:
             fn = getattr(lib, fn_name)
             fn.argtypes = argtypes
-            fn.restype = c_int
+            fn.restype = _RESTYPES.get(fn_name, c_int)
             _functions[fn_name] = fn
 
 
@@ -1269,8 +1274,18 @@ def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype, gate_activation=
     return out
 
 
+# How the recurrence with a constant decay runs: "auto" (default), in chunks (three kernels of float32 products, see
+# csrc/recurrent.cu) when some request of the step brings at least _CHUNKED_FROM tokens and the key size allows, token by
+# token otherwise; "tokens": token by token always.
+decay_scan_kernels = os.environ.get("AKAS_B200_DECAY_SCAN", "auto")
+if decay_scan_kernels not in ("auto", "tokens"):
+    raise ValueError(f"AKAS_B200_DECAY_SCAN must be auto or tokens, got {decay_scan_kernels!r}")
+_CHUNKED_FROM = 48
+
+
 @_flushes
-def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_scale, activation=None, write=True):
+def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_scale, activation=None, write=True, longest=None):
+    """``longest``: the most tokens a request brings in this step, where the caller knows it (it chooses the kernel)."""
     n = q.shape[0]
     if q.dtype != k.dtype or q.dtype != v.dtype or decay.dtype != torch.float32 or decay.numel() != heads:
         raise ValueError("decay_scan takes q, k, v of one dtype and a float32 decay per head")
@@ -1279,6 +1294,15 @@ def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_sca
     (qp, ldq), (kp, ldk), (vp, ldv) = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
     sp, stride = _slot_rows(state, "state")
     out = torch.empty((n, heads * vdim), dtype=torch.float32, device=q.device)
+    if decay_scan_kernels == "auto" and longest is not None and longest >= _CHUNKED_FROM:
+        words = int(_fn("recurrent", "akas_decay_chunk_scratch")(n, slots.numel(), heads, dim, vdim))
+        if words:
+            scratch = torch.empty(words, dtype=torch.float32, device=q.device)
+            _check(_fn("recurrent", "akas_decay_scan_chunked")(
+                qp, ldq, kp, ldk, vp, ldv, _ptr(decay), sp, stride, _ptr(cu_seqlens), _ptr(slots), _ptr(out), _ptr(scratch), n,
+                slots.numel(), heads, dim, vdim, float(q_scale), int(activation == "silu"), int(bool(write)), _code(q), _stream()),
+                "decay_scan (chunks)", kernels=3)
+            return out
     _check(_fn("recurrent", "akas_decay_scan")(qp, ldq, kp, ldk, vp, ldv, _ptr(decay), sp, stride, _ptr(cu_seqlens), _ptr(slots),
                                               _ptr(out), n, slots.numel(), heads, dim, vdim, float(q_scale),
                                               int(activation == "silu"), int(bool(write)), _code(q), _stream()), "decay_scan")

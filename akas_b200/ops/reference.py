@@ -300,7 +300,7 @@ def gla_scan(q, k, v, alpha, state, cu_seqlens, slots, heads, dim, vdim, q_scale
     return o.reshape(n, heads * vdim)
 
 
-def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_scale, activation=None, write=True):
+def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_scale, activation=None, write=True, longest=None):
     """Per request and head, token by token: S <- decay_h S + k_t v_t^T; o_t = S^T (q_scale q_t) with one constant
     decay per head (float32 [heads]); ``activation="silu"``: q, k and v pass silu first.
     q, k [N, heads * dim], v [N, heads * vdim] -> o float32 [N, heads * vdim]; state [slots, heads, vdim, dim]."""

@@ -138,7 +138,7 @@ class DecayedLinearAttention(Mixer):
         q, k, v = proj[:, :hd], proj[:, hd : 2 * hd], proj[:, 2 * hd : 2 * hd + hv]
         gate = proj[:, 2 * hd + hv : 2 * hd + 2 * hv]
         o = ops.decay_scan(q, k, v, self.decay, cache.state, ctx.cu_seqlens, ctx.slots, s.num_heads, s.key_dim, s.value_dim,
-                           s.q_scale, activation=s.activation, write=write)
+                           s.q_scale, activation=s.activation, write=write, longest=getattr(ctx, "max_query_len", None))
         heads, width = (1, hv) if s.whole_norm else (s.num_heads, s.value_dim)
         return ops.gated_rmsnorm(o, self.norm, s.norm_eps, gate, heads, width, self.rt.dtype,
                                  gate_activation=s.gate_activation, out=out, out_scale=out_scale)

@@ -458,7 +458,7 @@ def test_decay_scan_kernel(heads, dim, vdim, dtype):
 
     cuda.require(["recurrent"])
     g = torch.Generator().manual_seed(heads * 1000 + dim)
-    lengths, slots = [37, 1, 0, 18], [2, 0, -1, 3]
+    lengths, slots = [137, 1, 0, 64, 70], [2, 0, -1, 3, 4]  # more than two chunks, one token, none, a chunk exactly, a chunk and a bit
     n = sum(lengths)
     proj = (torch.randn(n, 2 * heads * dim + heads * vdim + 3, generator=g) * 0.7).to(dtype).cuda()
     q, k, v = proj[:, : heads * dim], proj[:, heads * dim : 2 * heads * dim], proj[:, 2 * heads * dim : 2 * heads * dim + heads * vdim]
@@ -470,10 +470,16 @@ def test_decay_scan_kernel(heads, dim, vdim, dtype):
         s_ref, s_got = state.clone(), state.clone()
         want = reference.decay_scan(q, k, v, decay, s_ref, cu, sl, heads, dim, vdim, 0.5, activation=act, write=write)
         got = cuda.decay_scan(q, k, v, decay, s_got, cu, sl, heads, dim, vdim, 0.5, activation=act, write=write)
-        live = torch.cat([torch.arange(0, 38), torch.arange(38, 56)])
+        live = torch.arange(0, n)
         _close(got[live], want[live], 2e-5, "scan o")
         _close(s_got, s_ref, 2e-5, "scan state")
         assert write or torch.equal(s_got, state)
+        # the same in chunks (what a step with a long portion runs)
+        s_chunk = state.clone()
+        got = cuda.decay_scan(q, k, v, decay, s_chunk, cu, sl, heads, dim, vdim, 0.5, activation=act, write=write, longest=max(lengths))
+        _close(got[live], want[live], 3e-5, "scan o, in chunks")
+        _close(s_chunk, s_ref, 3e-5, "scan state, in chunks")
+        assert write or torch.equal(s_chunk, state)
 
 
 @pytest.mark.gpu
