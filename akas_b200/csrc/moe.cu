@@ -20,6 +20,7 @@ namespace {
 
 constexpr int kRouteTokens = 8;   // tokens of a router block = its warps
 constexpr int kRouteChunk = 2048; // channels of h staged at a time (64 KB of float32 rows for the block's tokens)
+constexpr int kRouteOutputs = 4;  // router outputs whose rows a warp reads at the same time
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 
@@ -32,6 +33,7 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
   float* z = rows + kRouteTokens * kRouteChunk;    // [kRouteTokens][R] logits, then scores
   float* pick = z + kRouteTokens * R;              // [kRouteTokens][R] choice scores
   float* gbest = pick + kRouteTokens * R;          // [kRouteTokens][groups]
+  float* part = gbest + kRouteTokens * groups;     // [warps][kRouteOutputs][kRouteTokens] the warps' partial sums
   const int n0 = blockIdx.x * kRouteTokens;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < kRouteTokens * R; i += blockDim.x) z[i] = 0.f;
@@ -54,37 +56,71 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
       }
     }
     __syncthreads();
-    // a warp takes every eighth router output: its row of w once, 16 bytes a lane and several loads in flight, against
-    // the block's token rows in shared memory; the order of a (token, output) sum depends on the width only
+    // Warp w takes the w-th eighth of the staged channels for EVERY router output, so that all of a lane's loads of
+    // the matrix are in flight at once (one trip to memory instead of one per output); the warps' partial sums meet
+    // in shared memory and are added in the order of the warps: the order of a (token, output) sum depends on the
+    // width only.
     const bool vec = C % 4 == 0 && ((uintptr_t)w % 16) == 0;
-    for (int e = warp; e < R; e += kRouteTokens) {
-      float acc[kRouteTokens];
+    const int slice = ((width + kRouteTokens - 1) / kRouteTokens + 3) / 4 * 4;
+    const int s0 = min(width, warp * slice), s1 = min(width, s0 + slice);
+    for (int e0 = 0; e0 < R; e0 += kRouteOutputs) {
+      float acc[kRouteOutputs][kRouteTokens];
 #pragma unroll
-      for (int t = 0; t < kRouteTokens; ++t) acc[t] = 0.f;
-      const float* wr = w + (size_t)e * C + c0;
+      for (int o = 0; o < kRouteOutputs; ++o)
+#pragma unroll
+        for (int t = 0; t < kRouteTokens; ++t) acc[o][t] = 0.f;
       if (vec) {
-#pragma unroll 4
-        for (int c = lane * 4; c < width; c += 128) {
-          const float4 wv = *reinterpret_cast<const float4*>(wr + c);
+        for (int c = s0 + lane * 4; c < s1; c += 128) {
+          float4 wv[kRouteOutputs];
+#pragma unroll
+          for (int o = 0; o < kRouteOutputs; ++o)
+            wv[o] = e0 + o < R ? *reinterpret_cast<const float4*>(w + (size_t)(e0 + o) * C + c0 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
           for (int t = 0; t < kRouteTokens; ++t) {
             const float4 hv = *reinterpret_cast<const float4*>(rows + t * kRouteChunk + c);
-            acc[t] = fmaf(hv.x, wv.x, acc[t]); acc[t] = fmaf(hv.y, wv.y, acc[t]);
-            acc[t] = fmaf(hv.z, wv.z, acc[t]); acc[t] = fmaf(hv.w, wv.w, acc[t]);
+#pragma unroll
+            for (int o = 0; o < kRouteOutputs; ++o) {
+              acc[o][t] = fmaf(hv.x, wv[o].x, acc[o][t]); acc[o][t] = fmaf(hv.y, wv[o].y, acc[o][t]);
+              acc[o][t] = fmaf(hv.z, wv[o].z, acc[o][t]); acc[o][t] = fmaf(hv.w, wv[o].w, acc[o][t]);
+            }
           }
         }
       } else {
-        for (int c = lane; c < width; c += 32) {
-          const float wv = wr[c];
+        for (int c = s0 + lane; c < s1; c += 32) {
 #pragma unroll
-          for (int t = 0; t < kRouteTokens; ++t) acc[t] = fmaf(rows[t * kRouteChunk + c], wv, acc[t]);
+          for (int o = 0; o < kRouteOutputs; ++o) {
+            const float wv = e0 + o < R ? w[(size_t)(e0 + o) * C + c0 + c] : 0.f;
+#pragma unroll
+            for (int t = 0; t < kRouteTokens; ++t) acc[o][t] = fmaf(rows[t * kRouteChunk + c], wv, acc[o][t]);
+          }
         }
       }
+      // the lanes' 32 sums each (4 outputs x 8 tokens) are added across the warp so that lane l ends with the total of
+      // sum number l: every round a lane hands one half of what it still holds to its partner and keeps the other
+      // (31 shuffles instead of 32 x 5); the order of the additions is the same for every token and batch
+      static_assert(kRouteOutputs * kRouteTokens == 32, "one sum per lane");
+      float* v = &acc[0][0];
 #pragma unroll
-      for (int t = 0; t < kRouteTokens; ++t) {
-        const float sum = warp_sum(acc[t]);
-        if (lane == 0) z[t * R + e] += sum;
+      for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+          const float send = upper ? v[i] : v[i + n / 2];
+          const float keep = upper ? v[i + n / 2] : v[i];
+          v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
       }
+      part[warp * 32 + lane] = v[0];  // [warp][output][token]
+      __syncthreads();
+      for (int i = threadIdx.x; i < kRouteOutputs * kRouteTokens; i += blockDim.x) {
+        const int o = i / kRouteTokens, t = i % kRouteTokens;
+        if (e0 + o < R) {
+          float sum = z[t * R + e0 + o];
+          for (int ww = 0; ww < kRouteTokens; ++ww) sum += part[(ww * kRouteOutputs + o) * kRouteTokens + t];
+          z[t * R + e0 + o] = sum;
+        }
+      }
+      __syncthreads();
     }
   }
   __syncthreads();
@@ -239,7 +275,8 @@ AKAS_API int akas_moe_route(const void* h, long long ldh, const float* w, const 
   if (N <= 0) return 0;
   if (R <= 0 || groups <= 0 || R % groups || keep <= 0 || keep > groups || top <= 0 || top > keep * (R / groups))
     return (int)cudaErrorInvalidValue;
-  const size_t smem = sizeof(float) * ((size_t)kRouteTokens * kRouteChunk + 2 * (size_t)kRouteTokens * R + (size_t)kRouteTokens * groups);
+  const size_t smem = sizeof(float) * ((size_t)kRouteTokens * kRouteChunk + 2 * (size_t)kRouteTokens * R + (size_t)kRouteTokens * groups +
+                                       (size_t)kRouteTokens * kRouteOutputs * kRouteTokens);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   const dim3 grid((N + kRouteTokens - 1) / kRouteTokens);
   static size_t allowed[64][2] = {};

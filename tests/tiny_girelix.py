@@ -16,9 +16,12 @@ LEFT = dict(heads=6, kv_heads=2, dim=24, vdim=24, scale=0.31, rot=dict(base=1000
 LEFT_FULL = dict(heads=4, kv_heads=4, dim=16, vdim=16, scale=0.4, rot=dict(base=500.0, dims=16))
 LEFT_ODD = dict(heads=3, kv_heads=1, dim=20, vdim=20, scale=0.27, rot=dict(base=1000000.0, dims=6))
 LEFT_WIDE = dict(heads=36, kv_heads=2, dim=8, vdim=8, scale=0.5, rot=dict(base=100.0, dims=0))
+LEFT_RAGGED = dict(heads=3, kv_heads=3, dim=12, vdim=12, scale=0.33, rot=dict(base=77.0, dims=4))
 RIGHT = dict(heads=3, dim=20, vdim=24, decay=[0.55, 0.9, 0.995])
 RIGHT_ONE = dict(heads=1, dim=72, vdim=40, decay=[0.97])
 RIGHT_SMALL = dict(heads=2, dim=8, vdim=5, decay=[1.0, 0.25])
+RIGHT_RAGGED = dict(heads=2, dim=12, vdim=10, decay=[0.8, 0.99])
+RIGHT_LONG = dict(heads=1, dim=136, vdim=72, decay=[0.98])  # keys longer than the chunked recurrence takes
 
 
 def moe(experts, identity, top, count, keep, ff):
@@ -43,10 +46,13 @@ CONFIGS = {
     ]),
     "odd": model(52, 90, [layer(LEFT_ODD, RIGHT_SMALL, moe(7, 1, 2, 2, 1, 20)), layer(LEFT, RIGHT_ONE, moe(3, 1, 4, 1, 1, 36))],
                  eps=1e-6, mult=1.0),
+    # sizes that are multiples of nothing much: rows of 50 and 77, heads of 12, experts of 10
+    "ragged": model(50, 77, [layer(LEFT_RAGGED, RIGHT_RAGGED, moe(3, 0, 2, 1, 1, 10)), layer(LEFT_ODD, RIGHT_LONG, moe(4, 2, 2, 3, 2, 14))],
+                    eps=1e-3, mult=-0.8),
     "bare": model(48, 120, [layer(LEFT_FULL, RIGHT, None), layer(LEFT, RIGHT_SMALL, None)], mult=0.9),
 }
-PAGE = {"mix": 8, "odd": 16, "bare": 64}
-LENGTHS = {"mix": [1, 45, 2, 97, 33, 130, 64], "odd": [70, 3, 41, 100], "bare": [90, 1, 37]}
+PAGE = {"mix": 8, "odd": 16, "ragged": 32, "bare": 64}
+LENGTHS = {"mix": [1, 45, 2, 97, 33, 130, 64], "odd": [70, 3, 41, 100], "ragged": [75, 2, 140], "bare": [90, 1, 37]}
 TOL = {"float32": 3e-5, "bfloat16": 3e-2}  # largest |difference| over largest |reference logit|
 # A routing margin (in units of the scores, which lie in 0..1) below this may fall the other way in bfloat16, the more
 # so in a late layer, whose input carries the rounding of the layers before it.
