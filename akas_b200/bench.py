@@ -352,7 +352,7 @@ def bench_experts(tokens: int, c: int, f: int, experts: int = 14, identity: int 
         gemm = ops._fn("moe_grouped", "akas_moe_grouped_gemm")
         up = lambda: gemm(p(srt), p(w_gate_up), p(act), p(tile_expert), p(plan), cap, experts, 2 * f, c, 2, st())
         down = lambda: gemm(p(act), p(w_down), p(y), p(tile_expert), p(plan), cap, experts, c, f, 1, st())
-        comb = lambda: ops._fn("moe_grouped", "akas_moe_combine")(p(h), c, p(y), p(row_of_pair), p(weights), p(out), tokens, top, c, st())
+        comb = lambda: ops._fn("moe_grouped", "akas_moe_combine")(p(h), c, p(y), p(row_of_pair), p(weights), p(out), tokens, top, c, None, None, None, None, 0.0, st())
         sort()
         for name, fn, work in (("sort_ms", sort, 0.0), ("gate_up_ms", up, 2.0 * real * 2 * c * f), ("down_ms", down, 2.0 * real * c * f),
                                ("combine_ms", comb, 0.0)):

@@ -229,12 +229,15 @@ moe_gate_up_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__
   }
 }
 
-// One warp per (token, output channel c): the weighted sum over the token's chosen outputs.
+// One warp per (token, output channel c): the weighted sum over the token's chosen outputs. With `x` the sum does not
+// go to `out` but into the residual stream: x += mult * (ls_a * a + ls_b * sum), the update of a block whose mixer's
+// result a and feed-forward meet the stream together (a null scale is all ones).
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_down, const int* __restrict__ chosen,
                 const float* __restrict__ weights, const T* __restrict__ act, float* __restrict__ out, int top, int C, int F,
-                int experts) {
+                int experts, float* __restrict__ x, const float* __restrict__ a_res, const float* __restrict__ ls_a,
+                const float* __restrict__ ls_b, float mult) {
   const int n = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   constexpr int N = Vec<T>::N;
@@ -264,7 +267,14 @@ moe_down_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_
       }
       total = fmaf(g, warp_sum(acc), total);
     }
-    if (lane == 0) out[(size_t)n * C + c] = total;
+    if (lane == 0) {
+      if (x != nullptr) {
+        const size_t at = (size_t)n * C + c;
+        x[at] = fmaf(mult, fmaf(ls_b ? ls_b[c] : 1.f, total, (ls_a ? ls_a[c] : 1.f) * a_res[at]), x[at]);
+      } else {
+        out[(size_t)n * C + c] = total;
+      }
+    }
   }
 }
 
@@ -311,13 +321,13 @@ AKAS_API int akas_moe_gate_up(const void* h, long long ldh, const void* w_gate_u
 }
 
 AKAS_API int akas_moe_down(const void* h, long long ldh, const void* w_down, const int* chosen, const float* weights,
-                           const void* act, float* out, int N, int top, int C, int F, int experts, int dtype,
-                           cudaStream_t stream) {
+                           const void* act, float* out, int N, int top, int C, int F, int experts, int dtype, float* x,
+                           const float* a_res, const float* ls_a, const float* ls_b, float mult, cudaStream_t stream) {
   if (N <= 0) return 0;
   const dim3 grid(N, max(1, min((C + 7) / 8, N >= 2048 ? 2 : N >= 64 ? 32 : 256)));
   if (dtype == AKAS_F32)
     return launch_ordinary(moe_down_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, ldh, (const float*)w_down, chosen,
-                           weights, (const float*)act, out, top, C, F, experts);
+                           weights, (const float*)act, out, top, C, F, experts, x, a_res, ls_a, ls_b, mult);
   return launch_ordinary(moe_down_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, ldh, (const bf16*)w_down, chosen,
-                         weights, (const bf16*)act, out, top, C, F, experts);
+                         weights, (const bf16*)act, out, top, C, F, experts, x, a_res, ls_a, ls_b, mult);
 }

@@ -11,7 +11,7 @@
 //                come from the stacked matrices [experts * rows, K] at the tile's expert;
 //                  SWIGLU: act[row, F] = silu(gate) * up, bfloat16;   F32: y[row, C] = act . W_down^T, float32.
 //   moe_combine  out[n] = sum_k weight[n, k] * (y[row of pair (n, k)], or h[n] for an identity expert), in the
-//                order of the choice, float32.
+//                order of the choice, float32; or, given the residual stream x, x += mult * (ls_a * a + ls_b * that sum).
 // Every output is a sum over the inner size in the tile order of K, whatever the step holds beside the token, so a
 // token's result does not depend on the batch. Waits are bounded as in gemm_tcgen05.cu (akas_moe_grouped_status).
 #include <math.h>
@@ -76,7 +76,8 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, long long ldh, con
 
 __global__ void moe_combine_kernel(const bf16* __restrict__ h, long long ldh, const float* __restrict__ y,
                                    const int* __restrict__ row_of_pair, const float* __restrict__ weights,
-                                   float* __restrict__ out, int top, int C) {
+                                   float* __restrict__ out, int top, int C, float* __restrict__ x, const float* __restrict__ a_res,
+                                   const float* __restrict__ ls_a, const float* __restrict__ ls_b, float mult) {
   const int n = blockIdx.x;
   for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
     float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -94,7 +95,17 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ h, long long ldh, co
       total.x = fmaf(g, v.x, total.x); total.y = fmaf(g, v.y, total.y);
       total.z = fmaf(g, v.z, total.z); total.w = fmaf(g, v.w, total.w);
     }
-    *reinterpret_cast<float4*>(out + (size_t)n * C + c) = total;
+    if (x != nullptr) {
+      const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+      const float4 la = ls_a ? *reinterpret_cast<const float4*>(ls_a + c) : one, lb = ls_b ? *reinterpret_cast<const float4*>(ls_b + c) : one;
+      const float4 av = *reinterpret_cast<const float4*>(a_res + (size_t)n * C + c);
+      float4 xv = *reinterpret_cast<float4*>(x + (size_t)n * C + c);
+      xv.x = fmaf(mult, fmaf(lb.x, total.x, la.x * av.x), xv.x); xv.y = fmaf(mult, fmaf(lb.y, total.y, la.y * av.y), xv.y);
+      xv.z = fmaf(mult, fmaf(lb.z, total.z, la.z * av.z), xv.z); xv.w = fmaf(mult, fmaf(lb.w, total.w, la.w * av.w), xv.w);
+      *reinterpret_cast<float4*>(x + (size_t)n * C + c) = xv;
+    } else {
+      *reinterpret_cast<float4*>(out + (size_t)n * C + c) = total;
+    }
   }
 }
 
@@ -323,11 +334,13 @@ AKAS_API int akas_moe_grouped_gemm(const void* x, const void* w, void* y, const 
 }
 
 AKAS_API int akas_moe_combine(const void* h, long long ldh, const float* y, const int* row_of_pair, const float* weights,
-                              float* out, int N, int top, int C, cudaStream_t stream) {
+                              float* out, int N, int top, int C, float* x, const float* a_res, const float* ls_a,
+                              const float* ls_b, float mult, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (C % 8 || ldh % 4 || (uintptr_t)h % 8 || (uintptr_t)y % 16 || (uintptr_t)out % 16) return (int)cudaErrorInvalidValue;
+  if (((uintptr_t)x | (uintptr_t)a_res | (uintptr_t)ls_a | (uintptr_t)ls_b) % 16) return (int)cudaErrorInvalidValue;
   return launch_ordinary(moe_combine_kernel, dim3(N), dim3(C >= 1024 ? 256 : 128), 0, stream, (const bf16*)h, ldh, y, row_of_pair,
-                         weights, out, top, C);
+                         weights, out, top, C, x, a_res, ls_a, ls_b, mult);
 }
 
 AKAS_API int akas_moe_grouped_status() {

@@ -46,7 +46,7 @@ _SIGNATURES = {
         "akas_moe_gate_up": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                              c_void_p],
         "akas_moe_down": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_void_p],
+                          c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
     },
     "recurrent": {
         "akas_decay_gates": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -89,7 +89,8 @@ _SIGNATURES = {
         "akas_moe_sort": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                           c_void_p],
         "akas_moe_grouped_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "akas_moe_combine": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_moe_combine": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                             c_void_p, c_void_p, c_float, c_void_p],
         "akas_moe_grouped_status": [],
     },
     "conv": {
@@ -1426,7 +1427,18 @@ def moe_grouped_status() -> int:
     return int(_fn("moe_grouped", "akas_moe_grouped_status")())
 
 
-def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights):
+def _update_args(update, n, c):
+    """(x, a, scale_a, scale_b, mult) of a residual update as the kernels take it (null pointers and 0 for none)."""
+    if update is None:
+        return None, None, None, None, 0.0
+    x, a, scale_a, scale_b, mult = update
+    for t in (x, a):
+        if t.dtype != torch.float32 or t.shape != (n, c) or not t.is_contiguous():
+            raise ValueError("a residual update takes dense float32 tensors [N, C]")
+    return _ptr(x), _ptr(a), _ptr(scale_a), _ptr(scale_b), float(mult)
+
+
+def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, update=None):
     n, c = h.shape
     experts, f2, _ = w_gate_up.shape
     f, top = f2 // 2, chosen.shape[1]
@@ -1439,7 +1451,7 @@ def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights):
     rows = torch.empty((cap, c), dtype=h.dtype, device=dev)
     act = torch.empty((cap, f), dtype=h.dtype, device=dev)
     y = torch.empty((cap, c), dtype=torch.float32, device=dev)
-    out = torch.empty((n, c), dtype=torch.float32, device=dev)
+    out = torch.empty((n, c), dtype=torch.float32, device=dev) if update is None else update[0]
     _check(_fn("moe_grouped", "akas_moe_sort")(hp, ldh, _ptr(chosen), _ptr(row_of_pair), _ptr(tile_expert), _ptr(plan), _ptr(rows),
                                               n, top, c, experts, _stream()), "moe_sort", kernels=2)
     gemm = _fn("moe_grouped", "akas_moe_grouped_gemm")
@@ -1448,12 +1460,15 @@ def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights):
     _check(gemm(_ptr(act), _ptr(w_down), _ptr(y), _ptr(tile_expert), _ptr(plan), cap, experts, c, f, 1, _stream()),
            "grouped down product")
     _check(_fn("moe_grouped", "akas_moe_combine")(hp, ldh, _ptr(y), _ptr(row_of_pair), _ptr(weights), _ptr(out), n, top, c,
-                                                 _stream()), "moe_combine")
+                                                 *_update_args(update, n, c), _stream()), "moe_combine")
     return out
 
 
 @_flushes
-def moe_experts(h, w_gate_up, w_down, chosen, weights):
+def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None):
+    """The weighted sum of the chosen experts' results, float32 [N, C]. With ``update`` = (x, a, scale_a, scale_b, mult)
+    the sum is not returned but added into the residual stream by the last kernel: x += mult * (scale_a * a + scale_b *
+    sum), in place; returns x."""
     n, c = h.shape
     experts, f2, _ = w_gate_up.shape
     f, top = f2 // 2, chosen.shape[1]
@@ -1463,13 +1478,13 @@ def moe_experts(h, w_gate_up, w_down, chosen, weights):
     if (moe_kernels == "auto" and h.dtype == torch.bfloat16 and n * top > _MOE_SIMPLE_PAIRS and ldh % 8 == 0 and hp % 16 == 0
             and _fn("moe_grouped", "akas_moe_grouped_takes")(c, f, experts)):
         _dense(w_gate_up, "w_gate_up"), _dense(w_down, "w_down")
-        return _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights)
+        return _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, update)
     act = torch.empty((n * top, f), dtype=h.dtype, device=h.device)
-    out = torch.empty((n, c), dtype=torch.float32, device=h.device)
+    out = torch.empty((n, c), dtype=torch.float32, device=h.device) if update is None else update[0]
     _check(_fn("moe", "akas_moe_gate_up")(hp, ldh, _ptr(_dense(w_gate_up, "w_gate_up")), _ptr(chosen), _ptr(act), n, top, c, f,
                                          experts, _code(h), _stream()), "moe_gate_up")
     _check(_fn("moe", "akas_moe_down")(hp, ldh, _ptr(_dense(w_down, "w_down")), _ptr(chosen), _ptr(weights), _ptr(act),
-                                      _ptr(out), n, top, c, f, experts, _code(h), _stream()), "moe_down")
+                                      _ptr(out), n, top, c, f, experts, _code(h), *_update_args(update, n, c), _stream()), "moe_down")
     return out
 
 

@@ -511,8 +511,9 @@ def moe_route(h, w_router, correction, groups, keep, top):
     return chosen.to(torch.int32), w
 
 
-def moe_experts(h, w_gate_up, w_down, chosen, weights):
-    """out[n] = sum_k weights[n, k] * expert_(chosen[n, k])(h[n]) in float32 [N, C]. Expert e < E computes
+def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None):
+    """With ``update`` = (x, a, scale_a, scale_b, mult): x += mult * (scale_a * a + scale_b * out) in place, returns x. Else
+    out[n] = sum_k weights[n, k] * expert_(chosen[n, k])(h[n]) in float32 [N, C]. Expert e < E computes
     w_down[e] (silu(gate) * up) with [gate; up] = w_gate_up[e] h (w_gate_up [E, 2 F, C], w_down [E, C, F]; the hidden
     activations are rounded to h's dtype, as the kernels round them); an expert number from E on returns h itself."""
     n, c = h.shape
@@ -529,6 +530,9 @@ def moe_experts(h, w_gate_up, w_down, chosen, weights):
             gu = hf[rows] @ w_gate_up[e].to(torch.float32).T
             act = (torch.nn.functional.silu(gu[:, : f2 // 2]) * gu[:, f2 // 2 :]).to(h.dtype).to(torch.float32)
             out[rows] += g * (act @ w_down[e].to(torch.float32).T)
+    if update is not None:
+        x, a, scale_a, scale_b, mult = update
+        return scaled_add(x, a, scale_a, out, scale_b, mult)
     return out
 
 

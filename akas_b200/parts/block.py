@@ -38,6 +38,8 @@ def _float32_result(part, *args, **kwargs):
 def _parallel(block, h, ctx, cache, write):
     n = block.mixer_norm.forward(h)
     a = _float32_result(block.mixer, n, ctx, cache, residual=None, write=write)
+    if hasattr(block.ffn, "forward_update"):  # the feed-forward's last kernel does the block's update itself
+        return block.ffn.forward_update(n, ctx, h, a, block.mixer_scale, block.ffn_scale, block.spec.residual_multiplier)
     b = None if block.ffn is None else _float32_result(block.ffn, n, ctx, residual=None)
     return block.mixer.rt.ops.scaled_add(h, a, block.mixer_scale, b, block.ffn_scale, block.spec.residual_multiplier)
 

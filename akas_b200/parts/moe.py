@@ -60,6 +60,13 @@ class RoutedExperts(FeedForward):
         ).contiguous()
         self.w_down = torch.stack([get(self._n(f"e{e}.down")) for e in range(s.num_experts)]).contiguous()
 
+    def forward_update(self, x, ctx, h, a, scale_a, scale_b, mult):
+        """h += mult * (scale_a * a + scale_b * experts(x)) in place on the float32 residual stream h, by the experts' last
+        kernel: what a block whose sublayers' results meet the stream in one sum asks for."""
+        s, ops = self.spec, self.rt.ops
+        chosen, weights = ops.moe_route(x, self.w_router, self.correction, s.groups, s.keep_groups, s.top)
+        return ops.moe_experts(x, self.w_gate_up, self.w_down, chosen, weights, update=(h, a, scale_a, scale_b, mult))
+
     def forward(self, x, ctx, residual=None, out_dtype=None):
         s, ops = self.spec, self.rt.ops
         chosen, weights = ops.moe_route(x, self.w_router, self.correction, s.groups, s.keep_groups, s.top)

@@ -537,6 +537,12 @@ def test_routed_experts_kernels(outputs, experts, count, keep, top, c, f, dtype)
     want = reference.moe_experts(h, w_gate_up, w_down, want_c, want_w)
     got = cuda.moe_experts(h, w_gate_up, w_down, want_c, want_w)  # 45 tokens: the grouped product in bfloat16 where it takes the sizes
     _close(got, want, 2e-5 if dtype == torch.float32 else 1e-2, "experts")
+    # the residual update by the experts' last kernel against the plain sequence
+    x0, a0 = torch.randn(n, c, generator=g).cuda(), torch.randn(n, c, generator=g).cuda()
+    la, lb = torch.randn(c, generator=g).cuda(), torch.randn(c, generator=g).cuda()
+    for rows in (n, 5):
+        upd = cuda.moe_experts(h[:rows], w_gate_up, w_down, want_c[:rows], want_w[:rows], update=(x0[:rows].clone(), a0[:rows], la, lb, 0.7))
+        _close(upd, reference.scaled_add(x0[:rows].clone(), a0[:rows], la, want[:rows], lb, 0.7), 2e-5 if dtype == torch.float32 else 1e-2, "update")
     few = cuda.moe_experts(h[:5], w_gate_up, w_down, want_c[:5], want_w[:5])  # few pairs: token by token
     _close(few, want[:5], 2e-5 if dtype == torch.float32 else 1e-2, "experts, few tokens")
     if dtype == torch.bfloat16:
