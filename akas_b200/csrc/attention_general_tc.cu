@@ -314,28 +314,49 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
 }
 
 // One block per (request of one token, head): the parts' sums, rescaled to the common maximum (the sink's logit
-// included), added in the order of the parts; then the division, the gate and the constant.
+// included) and added in the order of the parts; then the division, the gate and the constant. The first warp reads
+// every part's maximum and weight sum at once (two parts a lane) and leaves a factor per part in shared memory.
 __global__ void general_merge_kernel(const float* __restrict__ partial, const int* __restrict__ cu_seqlens, bf16* __restrict__ out,
                                      Options opt, int H, int V, int splits) {
+  __shared__ float factor[64];
+  __shared__ float inv_s;
   const int token = cu_seqlens[blockIdx.x], head = blockIdx.y;
   const float* src = partial + ((size_t)token * H + head) * splits * (V + 2);
-  const bool sunk = opt.sink || opt.sinks != nullptr;
-  const float sink2 = opt.sinks != nullptr ? opt.sinks[head] * kLog2e : 0.f;
-  float top = sunk ? sink2 : -INFINITY;
-  for (int z = 0; z < splits; ++z) top = fmaxf(top, src[(size_t)z * (V + 2) + V]);
-  float denom = sunk ? exp2f(sink2 - top) : 0.f;
-  for (int z = 0; z < splits; ++z) {
-    const float m = src[(size_t)z * (V + 2) + V];
-    if (m != -INFINITY) denom += src[(size_t)z * (V + 2) + V + 1] * exp2f(m - top);
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const bool sunk = opt.sink || opt.sinks != nullptr;
+    const float sink2 = opt.sinks != nullptr ? opt.sinks[head] * kLog2e : 0.f;
+    float m[2], l[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int z = lane + 32 * i;
+      m[i] = z < splits ? src[(size_t)z * (V + 2) + V] : -INFINITY;
+      l[i] = z < splits ? src[(size_t)z * (V + 2) + V + 1] : 0.f;
+    }
+    float top = fmaxf(m[0], m[1]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    if (sunk) top = fmaxf(top, sink2);
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float f = m[i] == -INFINITY ? 0.f : exp2f(m[i] - top);
+      factor[lane + 32 * i] = f;
+      part = fmaf(l[i], f, part);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    const float denom = part + (sunk ? exp2f(sink2 - top) : 0.f);
+    float inv = denom > 0.f ? opt.out_scale / denom : 0.f;
+    if (opt.gate != nullptr) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[(size_t)token * opt.ldg + head])));
+    if (lane == 0) inv_s = inv;
   }
-  float inv = denom > 0.f ? opt.out_scale / denom : 0.f;
-  if (opt.gate != nullptr) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[(size_t)token * opt.ldg + head])));
+  __syncthreads();
+  const float inv = inv_s;
   for (int c = threadIdx.x; c < V; c += blockDim.x) {
     float acc = 0.f;
-    for (int z = 0; z < splits; ++z) {
-      const float m = src[(size_t)z * (V + 2) + V];
-      if (m != -INFINITY) acc = fmaf(src[(size_t)z * (V + 2) + c], exp2f(m - top), acc);
-    }
+#pragma unroll 8
+    for (int z = 0; z < splits; ++z) acc = fmaf(src[(size_t)z * (V + 2) + c], factor[z], acc);
     out[(size_t)token * opt.ldo + (size_t)head * V + c] = __float2bfloat16_rn(acc * inv);
   }
 }

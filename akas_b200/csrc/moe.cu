@@ -37,6 +37,14 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
   const int n0 = blockIdx.x * kRouteTokens;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < kRouteTokens * R; i += blockDim.x) z[i] = 0.f;
+  if (gridDim.x <= 16) {
+    // a step of few tokens is a few blocks that wait for memory: the whole matrix is asked into the L2 at once, so that
+    // the reads below, one group of outputs after another, do not each wait for DRAM
+    const char* bytes = reinterpret_cast<const char*>(w);
+    const size_t total = (size_t)R * C * sizeof(float);
+    for (size_t off = (size_t)threadIdx.x * 128; off < total; off += (size_t)blockDim.x * 128)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(bytes + off));
+  }
   for (int c0 = 0; c0 < C; c0 += kRouteChunk) {
     const int width = min(kRouteChunk, C - c0);
     __syncthreads();

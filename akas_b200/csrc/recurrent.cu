@@ -633,6 +633,43 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
   float ss = 0.f;
   if (V % 4 == 0 && ldg % 4 == 0 && ldo % 4 == 0 && sizeof(TO) == sizeof(TG) && (uintptr_t)gate % (4 * sizeof(TG)) == 0 &&
       (uintptr_t)out % (4 * sizeof(TO)) == 0) {
+    // four channels a lane: 16-byte reads of o, 8- or 16-byte reads of the gate and writes of the result. A row of at
+    // most 1,024 channels stays in registers between the sum and the result, with its weights and gates asked for in
+    // the same trip to memory (a step of few tokens is a handful of warps that only wait).
+    if (V <= 1024) {
+      float4 x[8], wv[8];
+      float gv[8][4];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int j = lane * 4 + i * 128;
+        if (j < V) {
+          x[i] = *reinterpret_cast<const float4*>(row + j);
+          wv[i] = *reinterpret_cast<const float4*>(w + j);
+          load4(gate + (size_t)n * ldg + (size_t)h * V + j, gv[i]);
+          ss = fmaf(x[i].x, x[i].x, ss); ss = fmaf(x[i].y, x[i].y, ss); ss = fmaf(x[i].z, x[i].z, ss); ss = fmaf(x[i].w, x[i].w, ss);
+        }
+      }
+      ss = warp_sum(ss);
+      const float inv = out_scale / sqrtf(ss / (float)V + eps);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int j = lane * 4 + i * 128;
+        if (j < V) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) gv[i][e] = sigmoid ? sigmoid_f(gv[i][e]) : gv[i][e] * sigmoid_f(gv[i][e]);
+          const float r[4] = {x[i].x * inv * wv[i].x * gv[i][0], x[i].y * inv * wv[i].y * gv[i][1], x[i].z * inv * wv[i].z * gv[i][2],
+                              x[i].w * inv * wv[i].w * gv[i][3]};
+          TO* dst = out + (size_t)n * ldo + (size_t)h * V + j;
+          if (sizeof(TO) == 4) {
+            *reinterpret_cast<float4*>(dst) = make_float4(r[0], r[1], r[2], r[3]);
+          } else {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(r[0], r[1]), b = __floats2bfloat162_rn(r[2], r[3]);
+            *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+          }
+        }
+      }
+      return;
+    }
     // four channels a lane: 16-byte reads of o, 8- or 16-byte reads of the gate and writes of the result
     for (int j = lane * 4; j < V; j += 128) {
       const float4 x = *reinterpret_cast<const float4*>(row + j);
