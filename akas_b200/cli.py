@@ -74,7 +74,9 @@ def _inspect(args):
     index = TensorIndex(args.model)
     check_inventory(model.params(), index)
     inventory = {name: dict(shape=list(shape), dtype=dtype) for name, (_, shape, dtype) in sorted(index.entries.items())}
-    print(json.dumps(dict(architecture=config.architecture, config=asdict(config), inventory=inventory), indent=2))
+    # a configuration that keeps its layers as nested tuples (so that it can be hashed) is shown as its config.json reads
+    shown = config.to_dict() if any(isinstance(v, tuple) for v in vars(config).values()) and hasattr(config, "to_dict") else asdict(config)
+    print(json.dumps(dict(architecture=config.architecture, config=shown, inventory=inventory), indent=2))
 
 
 def _generate(args):

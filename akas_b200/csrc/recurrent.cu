@@ -293,10 +293,41 @@ __device__ __forceinline__ bool find_chunk(const int* __restrict__ cu_seqlens, c
   return false;
 }
 
+// Stages `live` rows of `cols` channels (src row pitch ld) into shared memory rows of `pitch` floats as float32, silu'd
+// where `act`, times `scale` or, where `pw` is given, times pw[live - 1 - row]; rows from `live` to `rows` and the columns
+// from `cols` to `pitch` become zero. Eight channels a load where the sizes allow: a chunk's inputs are then two or
+// four loads a thread, all in flight together, where one channel a load made the block wait on memory most of its time.
 template <typename T>
-__device__ __forceinline__ float chunk_in(const T* p, int act) {
-  const float x = to_f32(*p);
-  return act ? x * sigmoid_f(x) : x;
+__device__ __forceinline__ void stage_rows(float* __restrict__ dst, int pitch, const T* __restrict__ src, long long ld, int live,
+                                           int cols, int rows, float scale, const float* __restrict__ pw, int act) {
+  const bool vec = cols % 8 == 0 && ld % 8 == 0 && ((uintptr_t)src % 16) == 0;
+  if (vec) {
+    const int per = cols / 8;
+    for (int i = threadIdx.x; i < rows * per; i += kChunkThreads) {
+      const int t = i / per, c = (i % per) * 8;
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (t < live) {
+        load8(src + (size_t)t * ld + c, v);
+        const float f = pw != nullptr ? pw[live - 1 - t] : scale;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (act ? v[j] * sigmoid_f(v[j]) : v[j]) * f;
+      }
+      *reinterpret_cast<float4*>(dst + t * pitch + c) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(dst + t * pitch + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+    const int pad = pitch - cols;
+    for (int i = threadIdx.x; i < rows * pad; i += kChunkThreads) dst[(i / pad) * pitch + cols + i % pad] = 0.f;
+    return;
+  }
+  for (int i = threadIdx.x; i < rows * pitch; i += kChunkThreads) {
+    const int t = i / pitch, c = i % pitch;
+    float x = 0.f;
+    if (t < live && c < cols) {
+      x = to_f32(src[(size_t)t * ld + c]);
+      x = (act ? x * sigmoid_f(x) : x) * (pw != nullptr ? pw[live - 1 - t] : scale);
+    }
+    dst[i] = x;
+  }
 }
 
 template <typename T>
@@ -307,18 +338,15 @@ chunk_state_kernel(const T* __restrict__ k, long long ldk, const T* __restrict__
   extern __shared__ __align__(16) float sm[];
   float* sk = sm;                    // [kChunk][DP]
   float* sv = sk + kChunk * DP;      // [kChunk][kChunkVT], already times a^(len - 1 - s)
+  float* pw = sv + kChunk * kChunkVT;  // [kChunk] powers of the decay
   int req, first, len, index;
   if (!find_chunk(cu_seqlens, slots, R, blockIdx.x, req, first, len, index)) return;
   const int h = blockIdx.y, v0 = blockIdx.z * kChunkVT;
   const double a = (double)decay[h];
-  for (int i = threadIdx.x; i < kChunk * DP; i += kChunkThreads) {
-    const int t = i / DP, d = i % DP;
-    sk[i] = t < len && d < D ? chunk_in(k + (size_t)(first + t) * ldk + (size_t)h * D + d, act) : 0.f;
-  }
-  for (int i = threadIdx.x; i < kChunk * kChunkVT; i += kChunkThreads) {
-    const int t = i / kChunkVT, c = v0 + i % kChunkVT;
-    sv[i] = t < len && c < V ? chunk_in(v + (size_t)(first + t) * ldv + (size_t)h * V + c, act) * (float)pow(a, (double)(len - 1 - t)) : 0.f;
-  }
+  for (int i = threadIdx.x; i < kChunk; i += kChunkThreads) pw[i] = (float)pow(a, (double)i);
+  __syncthreads();
+  stage_rows(sk, DP, k + (size_t)first * ldk + (size_t)h * D, ldk, len, D, kChunk, 1.f, nullptr, act);
+  stage_rows(sv, kChunkVT, v + (size_t)first * ldv + (size_t)h * V + v0, ldv, len, min(kChunkVT, V - v0), kChunk, 1.f, pw, act);
   __syncthreads();
   // a thread owns 4 value channels x 4 key channels at a time
   const int tv = (threadIdx.x / 16) * 4, td = (threadIdx.x % 16) * 4;  // 16 x 16 threads cover 64 x 64
@@ -395,56 +423,54 @@ chunk_output_kernel(const T* __restrict__ q, long long ldq, const T* __restrict_
   const int h = blockIdx.y, v0 = blockIdx.z * kChunkVT;
   const double a = (double)decay[h];
   for (int i = threadIdx.x; i <= kChunk; i += kChunkThreads) pw[i] = (float)pow(a, (double)i);
-  for (int i = threadIdx.x; i < kChunk * DP; i += kChunkThreads) {
-    const int t = i / DP, d = i % DP;
-    const bool in = t < len && d < D;
-    sq[i] = in ? chunk_in(q + (size_t)(first + t) * ldq + (size_t)h * D + d, act) * q_scale : 0.f;
-    sk[i] = in ? chunk_in(k + (size_t)(first + t) * ldk + (size_t)h * D + d, act) : 0.f;
-  }
-  const float* start = scratch + ((size_t)blockIdx.x * H + h) * V * D;
-  for (int i = threadIdx.x; i < kChunkVT * DP; i += kChunkThreads) {
-    const int c = v0 + i / DP, d = i % DP;
-    ss[i] = c < V && d < D ? start[(size_t)c * D + d] : 0.f;
-  }
-  for (int i = threadIdx.x; i < kChunk * kChunkVT; i += kChunkThreads) {
-    const int t = i / kChunkVT, c = v0 + i % kChunkVT;
-    sv[i] = t < len && c < V ? chunk_in(v + (size_t)(first + t) * ldv + (size_t)h * V + c, act) : 0.f;
-  }
+  stage_rows(sq, DP, q + (size_t)first * ldq + (size_t)h * D, ldq, len, D, kChunk, q_scale, nullptr, act);
+  stage_rows(sk, DP, k + (size_t)first * ldk + (size_t)h * D, ldk, len, D, kChunk, 1.f, nullptr, act);
+  // the state at the chunk's start: rows are this tile's value channels
+  stage_rows(ss, DP, scratch + ((size_t)blockIdx.x * H + h) * V * D + (size_t)v0 * D, (long long)D, min(kChunkVT, V - v0), D, kChunkVT,
+             1.f, nullptr, 0);
+  stage_rows(sv, kChunkVT, v + (size_t)first * ldv + (size_t)h * V + v0, ldv, len, min(kChunkVT, V - v0), kChunk, 1.f, nullptr, act);
   __syncthreads();
-  const int tr = (threadIdx.x / 16) * 4, tc = (threadIdx.x % 16) * 4;  // a thread's 4 rows x 4 columns of a 64 x 64 result
-  {  // scores of queries tr.. against keys tc.., times a^(t - s) on and below the diagonal
+  // A thread's part of a 64 x 64 result: rows tr .. tr + 3 and columns tc, tc + 16, tc + 32, tc + 48. Where a column
+  // is a row of shared memory (a key, a value channel of the state), the 8 threads of a quarter of a warp read 8
+  // neighbouring rows, whose 16-byte words lie in different banks (rows are DP = 4 mod 8 floats apart); with four
+  // neighbouring columns a thread, they would read rows 4 apart and meet in two banks.
+  const int tr = (threadIdx.x / 16) * 4, tc = threadIdx.x % 16;
+  {  // scores of queries tr.. against keys tc + 16 j, times a^(t - s) on and below the diagonal
     float acc[4][4] = {};
-    if (tc <= tr + 3) {
-      for (int d = 0; d < DP; d += 4) {
-        float4 qv[4], kv[4];
+    for (int d = 0; d < DP; d += 4) {
+      float4 qv[4], kv[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          qv[i] = *reinterpret_cast<const float4*>(sq + (tr + i) * DP + d);
-          kv[i] = *reinterpret_cast<const float4*>(sk + (tc + i) * DP + d);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[i][j] = fmaf(qv[i].x, kv[j].x, acc[i][j]); acc[i][j] = fmaf(qv[i].y, kv[j].y, acc[i][j]);
-            acc[i][j] = fmaf(qv[i].z, kv[j].z, acc[i][j]); acc[i][j] = fmaf(qv[i].w, kv[j].w, acc[i][j]);
-          }
+      for (int i = 0; i < 4; ++i) {
+        qv[i] = *reinterpret_cast<const float4*>(sq + (tr + i) * DP + d);
+        kv[i] = *reinterpret_cast<const float4*>(sk + (tc + 16 * i) * DP + d);
       }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(qv[i].x, kv[j].x, acc[i][j]); acc[i][j] = fmaf(qv[i].y, kv[j].y, acc[i][j]);
+          acc[i][j] = fmaf(qv[i].z, kv[j].z, acc[i][j]); acc[i][j] = fmaf(qv[i].w, kv[j].w, acc[i][j]);
+        }
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) sa[(tr + i) * kChunk + tc + j] = tc + j <= tr + i ? acc[i][j] * pw[tr + i - tc - j] : 0.f;
+      for (int j = 0; j < 4; ++j) {
+        const int key = tc + 16 * j;
+        sa[(tr + i) * kChunk + key] = key <= tr + i ? acc[i][j] * pw[tr + i - key] : 0.f;
+      }
   }
   __syncthreads();
-  float acc[4][4] = {};  // tokens tr.. x value channels tc..
+  float acc[4][4] = {};  // tokens tr.. x value channels tc + 16 j
   for (int t = 0; t < min(tr + 4, len); ++t) {  // keys up to the thread's last query
-    const float4 vv = *reinterpret_cast<const float4*>(sv + t * kChunkVT + tc);
+    float vv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) vv[j] = sv[t * kChunkVT + tc + 16 * j];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const float w = sa[(tr + i) * kChunk + t];
-      acc[i][0] = fmaf(w, vv.x, acc[i][0]); acc[i][1] = fmaf(w, vv.y, acc[i][1]);
-      acc[i][2] = fmaf(w, vv.z, acc[i][2]); acc[i][3] = fmaf(w, vv.w, acc[i][3]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(w, vv[j], acc[i][j]);
     }
   }
   float carry[4][4] = {};  // what the state at the chunk's start gives: S^T q, times a^(t + 1) below
@@ -453,7 +479,7 @@ chunk_output_kernel(const T* __restrict__ q, long long ldq, const T* __restrict_
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       qv[i] = *reinterpret_cast<const float4*>(sq + (tr + i) * DP + d);
-      sr[i] = *reinterpret_cast<const float4*>(ss + (tc + i) * DP + d);
+      sr[i] = *reinterpret_cast<const float4*>(ss + (tc + 16 * i) * DP + d);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -467,24 +493,24 @@ chunk_output_kernel(const T* __restrict__ q, long long ldq, const T* __restrict_
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j)
-      if (tr + i < len && v0 + tc + j < V)
-        out[(size_t)(first + tr + i) * ((size_t)H * V) + (size_t)h * V + v0 + tc + j] = fmaf(pw[tr + i + 1], carry[i][j], acc[i][j]);
+      if (tr + i < len && v0 + tc + 16 * j < V)
+        out[(size_t)(first + tr + i) * ((size_t)H * V) + (size_t)h * V + v0 + tc + 16 * j] = fmaf(pw[tr + i + 1], carry[i][j], acc[i][j]);
 }
 
 template <typename T>
 int launch_chunks(const T* q, long long ldq, const T* k, long long ldk, const T* v, long long ldv, const float* decay, float* state,
                   long long slot_stride, const int* cu_seqlens, const int* slots, float* out, float* scratch, int tokens,
                   int requests, int H, int D, int V, float q_scale, int act, int write, cudaStream_t stream) {
-  const int DP = (D + 3) / 4 * 4 + 4;  // rows of key channels in shared memory: whole 16-byte words, and a pad against bank conflicts
+  const int DP = (D + 7) / 8 * 8 + 4;  // rows of key channels in shared memory: whole 16-byte words, 4 mod 8 floats apart (see chunk_output)
   const int chunks = (tokens + kChunk - 1) / kChunk + requests;  // at most: every request may end with a part of a chunk
   const int vt = (V + kChunkVT - 1) / kChunkVT;
-  const size_t smem1 = sizeof(float) * ((size_t)kChunk * DP + kChunk * kChunkVT);
+  const size_t smem1 = sizeof(float) * ((size_t)kChunk * DP + kChunk * kChunkVT + kChunk);
   const size_t smem3 = sizeof(float) * ((size_t)2 * kChunk * DP + (size_t)kChunkVT * DP + kChunk * kChunkVT + kChunk * kChunk + kChunk + 4);
   static bool configured[64] = {};
   int device = 0;
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
   if (!configured[device]) {
-    const int most = (int)(sizeof(float) * ((size_t)2 * kChunk * (kChunkMaxD + 4) + (size_t)kChunkVT * (kChunkMaxD + 4) + kChunk * kChunkVT +
+    const int most = (int)(sizeof(float) * ((size_t)2 * kChunk * (kChunkMaxD + 12) + (size_t)kChunkVT * (kChunkMaxD + 12) + kChunk * kChunkVT +
                                            kChunk * kChunk + kChunk + 4));
     cudaError_t e = cudaFuncSetAttribute(chunk_output_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(chunk_output_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);

@@ -73,8 +73,9 @@ class Block:
         width = norm_param.shape
         if s.mixer_scale_name is not None:
             out[s.mixer_scale_name] = Param(width, role="vector", mean=1.0)
-        if s.ffn_scale_name is not None and self.ffn is not None:
-            out[s.ffn_scale_name] = Param(width, role="vector", mean=1.0)
+        if s.ffn_scale_name is not None:
+            # (a layer without a feed-forward: a checkpoint may still carry the scale that would follow one)
+            out[s.ffn_scale_name] = Param(width, role="vector", mean=1.0, optional=self.ffn is None)
         if self.ffn is not None and self.ffn_norm is not None:
             (norm_param,) = self.ffn_norm.params().values()
             out[s.ffn_norm_name] = norm_param

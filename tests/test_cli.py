@@ -58,3 +58,25 @@ def test_generate_and_bench_run(tmp_path, capsys):
           "--generated", "3", "--repeats", "1", "--baseline", str(earlier), "--max-regression", "0.99"])
     changes = json.loads(capsys.readouterr().out)["changes"]
     assert len(changes) == 2 and not any(change["regressed"] for change in changes)
+
+
+def test_random_and_inspect_take_a_girelix_configuration(tmp_path, capsys):
+    import tiny_girelix
+
+    main(["random", "--out", str(tmp_path / "g"), "--config", json.dumps(tiny_girelix.CONFIGS["odd"]), "--seed", "2"])
+    capsys.readouterr()
+    main(["inspect", "--model", str(tmp_path / "g")])
+    report = json.loads(capsys.readouterr().out)
+    assert report["architecture"] == "Girelix" and report["config"] == json.loads(json.dumps(tiny_girelix.CONFIGS["odd"]))
+    assert {"l0.mix.left.sink", "l1.mlp.e2.down", "l0.ls2", "head"} <= set(report["inventory"])
+
+
+@pytest.mark.gpu
+def test_generate_runs_a_girelix_folder(tmp_path, capsys):
+    import tiny_girelix
+
+    main(["random", "--out", str(tmp_path / "g"), "--config", json.dumps(tiny_girelix.CONFIGS["mix"]), "--seed", "2"])
+    capsys.readouterr()
+    for extra in ([], ["--temperature", "0.7", "--top-k", "20", "--seed", "2", "--dtype", "float32"]):
+        main(["generate", "--model", str(tmp_path / "g"), "--prompt", "5 17 3 9", "--max-tokens", "7", "--ignore-eos", *extra])
+        assert len(capsys.readouterr().out.split()) == 7
