@@ -15,6 +15,7 @@ latency too: src/akas/execution/forward.py:41-45).
 
 from __future__ import annotations
 
+import gc
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import numpy as np
@@ -365,8 +366,17 @@ class _DecodeGraph:
             graph = torch.cuda.CUDAGraph()
             ctx.memo = {"captured": True}
             before = getattr(runner.ops, "launch_count", 0)
-            with torch.cuda.graph(graph):
-                self.logits = runner.model.forward(ctx, runner.cache.views)
+            # Destroying a graph is not permitted while any stream captures and would invalidate the capture. Graphs of
+            # runners that are gone die when the collector finds them, so it runs now and rests until the capture ends.
+            gc.collect()
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self.logits = runner.model.forward(ctx, runner.cache.views)
+            finally:
+                if collecting:
+                    gc.enable()
             if self.lengths is None:
                 runner.kernels_per_decode_step[self.bucket] = getattr(runner.ops, "launch_count", 0) - before
             self.graph = graph
