@@ -16,7 +16,7 @@ import torch
 import plain_girelix as plain
 import traces
 
-from tiny_girelix import (CLOSE_CALL, CONFIGS, LEFT, LEFT_FULL, LEFT_ODD, LENGTHS, PAGE, RIGHT, RIGHT_ONE, RIGHT_SMALL, TOL,
+from tiny_girelix import (CLOSE_CALL, CONFIGS, LEFT, LEFT_FULL, LENGTHS, PAGE, RIGHT, RIGHT_SMALL, TOL,
                           layer, make_folder, model, moe, plant, prompts)
 
 
